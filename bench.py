@@ -1,0 +1,442 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: the chained per-pass op mix of one forward pass, token-sharded over N GPUs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference|reference-cuda]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+One step = one pass over a shard of 65,536 tokens per GPU (weak scaling): 1 embedding gather, 42 fused
+residual-add + RMSNorm, 21 gated RMSNorm, 17 relu^2 = 81 launches, 2,693,380 algorithmic HBM bytes per token.
+Rank 0 prints ONE JSON line.  `value` is device-timed whole-job tokens/s with every input resident in HBM;
+`e2e` is the same pass through the host-buffer call (ids copied in from pinned memory, result row copied
+back) timed by the wall clock; `roofline` describes the dominant kernel (add + RMSNorm) from CUDA events
+recorded around every launch of the timed region; `kernels` gives the same for the other three.
+
+--impl reference        the torch golden formulation on the host cores (all threads), a bounded token sample
+--impl reference-cuda   the reference's OWN CUDA kernels (recompiled for sm_100a into oracle/_ref) on the GPU,
+                        unfused as the reference runs them (add kernel, then rmsnorm kernel)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+METRIC = "achieved HBM GB/s (% of B200 peak) and tokens/s per fused op at 1/2/4/8 GPUs"
+TOKENS_PER_GPU = 65536
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+# algorithmic HBM bytes per token and per launch kind (each activation byte crosses HBM once)
+BYTES_PER_TOKEN = {"embedding": 2 * 3136 * 2 + 4, "add_rmsnorm": 4 * 3136 * 2, "gated_rmsnorm": 3 * 6144 * 2,
+                   "relu2": 2 * 12544 * 2}
+
+
+# ------------------------------------------------------------------------------------------------
+# rank plumbing (works with gloo on CPU and nccl on GPU)
+# ------------------------------------------------------------------------------------------------
+def _reduce(value: float, op) -> float:
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return value
+    dev = "cuda" if dist.get_backend() == "nccl" else "cpu"
+    t = torch.tensor([value], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=op)
+    return float(t.item())
+
+
+def max_over_ranks(value: float) -> float:
+    return _reduce(value, dist.ReduceOp.MAX)
+
+
+def sum_over_ranks(value: float) -> float:
+    return _reduce(value, dist.ReduceOp.SUM)
+
+
+def barrier() -> None:
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        dist.barrier()
+
+
+def measured_peak() -> tuple[float, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback (6650 GB/s, earlier measurement on this pool)"
+
+
+# ------------------------------------------------------------------------------------------------
+# clock sampling during the timed region
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.samples: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+        sel = []
+        try:
+            sel = ["-i", str(torch.cuda.get_device_properties(device_index).uuid)]
+            if not sel[1].startswith("GPU-"):
+                sel[1] = "GPU-" + sel[1]
+        except Exception:
+            sel = []
+        self.cmd = ["nvidia-smi", *sel, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"]
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(self.cmd, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self) -> None:
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        if self.thread:
+            self.thread.join(timeout=2)
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx.append(float(s[1]))
+                power.append(float(s[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, s[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+# the B200 arm
+# ------------------------------------------------------------------------------------------------
+class TracedChain:
+    """ChainPass whose ops record a CUDA event after every launch, so each launch's device time is known."""
+
+    def __init__(self, cp):
+        self.cp = cp
+        self.kinds: list[str] = []
+        self.events: list[torch.cuda.Event] = []
+
+    def run(self) -> None:
+        from nemotron_infer_b200 import chain, ops
+        cp, b = self.cp, self.cp.buf
+
+        def mark(kind):
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.kinds.append(kind)
+            self.events.append(ev)
+
+        mark("start")
+        cur, other = b.hidden
+        ops.embedding(b.table, b.ids, out=cur, err_flag=b.err_flag)
+        mark("embedding")
+        n_m = 0
+        for i, kind in enumerate(cp.schedule):
+            if kind == "M":
+                ops.rmsnorm_gated(b.y, b.z, b.gated_w[n_m], chain.D_INNER // chain.N_GROUPS, out=b.gated_out)
+                n_m += 1
+                mark("gated_rmsnorm")
+            elif kind == "-":
+                ops.relu2(b.u, out=b.act)
+                mark("relu2")
+            ops.add_rmsnorm(cur, b.mixer_out[i % len(b.mixer_out)], b.norm_w[i], out_res=other, out=b.normed)
+            mark("add_rmsnorm")
+            cur, other = other, cur
+
+    def per_kind_ms(self) -> dict[str, list[float]]:
+        out: dict[str, list[float]] = {}
+        for i in range(1, len(self.events)):
+            if self.kinds[i] == "start":
+                continue
+            out.setdefault(self.kinds[i], []).append(self.events[i - 1].elapsed_time(self.events[i]))
+        return out
+
+
+def cpu_chain_tokens_per_s(tokens: int, reps: int, threads: int) -> tuple[float, float]:
+    """Times the torch golden formulation of the same 81-op chain on the host cores."""
+    from oracle import torch_golden as og
+    from nemotron_infer_b200 import chain
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    bf = torch.bfloat16
+    vocab = 131072
+    table = torch.empty(vocab, chain.HIDDEN, dtype=bf)
+    for lo in range(0, vocab, 16384):
+        table[lo:lo + 16384] = (0.02 * torch.randn(16384, chain.HIDDEN, generator=g)).to(bf)
+    ids = torch.randint(0, vocab, (tokens,), generator=g)
+    mix = [torch.randn(tokens, chain.HIDDEN, generator=g).to(bf) for _ in range(2)]
+    y, z = (torch.randn(tokens, chain.D_INNER, generator=g).to(bf) for _ in range(2))
+    u = (2 * torch.randn(tokens, chain.INTER, generator=g)).to(bf)
+    nw = 1 + 0.1 * torch.randn(chain.N_LAYERS, chain.HIDDEN, generator=g)
+    gw = 1 + 0.1 * torch.randn(21, chain.D_INNER, generator=g)
+    sched = chain.layer_schedule()
+
+    def one_pass():
+        h = og.embedding(ids, table)
+        n_m = 0
+        for i, kind in enumerate(sched):
+            if kind == "M":
+                og.gated_rmsnorm_bf16(y, z, gw[n_m], chain.D_INNER // chain.N_GROUPS)
+                n_m += 1
+            elif kind == "-":
+                og.relu2_bf16(u)
+            h, n = og.add_rmsnorm_bf16(h, mix[i % 2], nw[i])
+        return n
+
+    one_pass()
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        one_pass()
+        times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return tokens / med, med * 1e3
+
+
+def run_b200(args, rank: int, world: int, local_rank: int) -> dict | None:
+    from nemotron_infer_b200 import _lib, chain, ops
+    lib = _lib.load()                       # raises if the CUDA library is missing: there is no fallback
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (B200); no CPU path exists for the product arm")
+    torch.cuda.set_device(local_rank)
+    _lib.check(lib.nmt_set_device(local_rank), "nmt_set_device")
+    T = args.tokens
+    cp = chain.ChainPass(T, f"cuda:{local_rank}", seed=1234 + rank)
+    for _ in range(max(args.warmup, 3)):
+        cp.run()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    traced = TracedChain(cp)
+    launches0 = ops.launch_count()
+    barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        traced.run()
+    ev1.record()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    launches = ops.launch_count() - launches0
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    tokens_total = sum_over_ranks(T) * args.steps
+    assert int(cp.buf.err_flag.item()) == 0
+
+    # end to end through the host-buffer call
+    ids_host = cp.buf.ids.cpu().pin_memory()
+    cp.run_from_host(ids_host)
+    barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cp.run_from_host(ids_host)
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+
+    per_kind = traced.per_kind_ms()
+    local = {k: (statistics.mean(v), len(v)) for k, v in per_kind.items()}
+    if rank != 0:
+        return None
+    peak, peak_src = measured_peak()
+    traffic = {}
+    tp = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if os.path.exists(tp):
+        traffic = json.load(open(tp))
+    kernels = {}
+    for kind, (mean_ms, n) in local.items():
+        bytes_launch = BYTES_PER_TOKEN[kind] * T
+        ach = bytes_launch / (mean_ms * 1e-3) / 1e9
+        t_tok = traffic.get(kind, {}).get("dram_bytes_per_token")
+        kernels[kind] = {"bound": "hbm", "achieved": round(ach, 1), "peak": peak, "unit": "GB/s",
+                         "frac": round(ach / peak, 4), "frac_of_nominal_8000": round(ach / NOMINAL_HBM_GBS, 4),
+                         "traffic": (t_tok * T if t_tok else None), "algorithmic_bytes": bytes_launch,
+                         "avg_launch_ms": round(mean_ms, 4), "launches": n,
+                         "tokens_per_s": round(T / (mean_ms * 1e-3), 1)}
+    value = tokens_total / (ms_total * 1e-3)
+    gbs = value * chain.bytes_per_token(4) / 1e9
+    out = {
+        "metric": METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_total / args.steps, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "BASELINE.json configs[4]: chained per-pass op mix (1 embedding gather, 42 add+RMSNorm "
+                               "@3136, 21 gated RMSNorm @6144/8 groups, 17 relu^2 @12544), token-sharded, no collective",
+                   "tokens_per_gpu": T, "global_tokens": int(tokens_total // args.steps), "ids": "int32",
+                   "bytes_per_token": chain.bytes_per_token(4),
+                   "l2": "every activation tensor (>= 411 MB) and the 822 MB table exceed the 126 MB L2; no flush"},
+        "hbm_gbs": round(gbs, 1), "hbm_gbs_per_gpu": round(gbs / world, 1),
+        "hbm_frac_of_measured_peak": round(gbs / world / peak, 4),
+        "hbm_frac_of_nominal_8000": round(gbs / world / NOMINAL_HBM_GBS, 4),
+        "roofline": dict(kernels["add_rmsnorm"], kernel="rmsnorm_rowwarp_kernel<13,true> (fused add+RMSNorm)",
+                         peak_source=peak_src),
+        "kernels": kernels,
+        "e2e": {"value": round(tokens_total / e2e_s, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": T * 4 * world, "d2h_bytes_per_step": 3136 * 2 * world,
+                "ms_per_step": round(e2e_s / args.steps * 1e3, 4),
+                "call": "ChainPass.run_from_host(ids in pinned host memory) -> last token's normed hidden state on the host"},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        v, ms = cpu_chain_tokens_per_s(args.cpu_tokens, 3, threads)
+        out["cpu_baseline"] = {"value": round(v, 1), "unit": "tokens/s", "cores": threads, "kind": "port",
+                               "sample": f"the same 81-op chain in the torch golden formulation (oracle/torch_golden.py) on "
+                                         f"{args.cpu_tokens} tokens, median of 3 passes after 1 warm-up, {ms:.0f} ms per pass, "
+                                         f"torch {torch.__version__} with {threads} threads"}
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arms
+# ------------------------------------------------------------------------------------------------
+def run_reference_cpu(args, world: int) -> dict:
+    threads = os.cpu_count() or 1
+    reps = max(args.steps, 1)
+    v, ms = cpu_chain_tokens_per_s(args.cpu_tokens, reps, threads)
+    sample = (f"reference formulation (tools/dump_*.py golden functions restated in oracle/torch_golden.py) of the "
+              f"81-op chain on {args.cpu_tokens} tokens per step, {threads} host threads, torch {torch.__version__}; "
+              f"the reference has no CPU implementation of these ops other than this torch formulation")
+    out = {"impl": "reference", "metric": METRIC, "value": round(v, 1), "unit": "tokens/s", "n_gpus": world,
+           "steps": reps, "warmup": 1, "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak",
+           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": "BASELINE.json configs[4] chained per-pass op mix, bounded sample",
+                      "tokens_per_step": args.cpu_tokens},
+           "cpu_baseline": {"value": round(v, 1), "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+           "e2e": {"value": round(v, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    if torch.cuda.is_available() and os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libnemotron_ref.so")):
+        try:
+            out["reference_cuda"] = run_reference_cuda(args, 0, quiet=True)
+        except Exception as e:  # the CPU figure stands on its own
+            out["reference_cuda"] = {"unavailable": f"{type(e).__name__}: {e}"}
+    return out
+
+
+def run_reference_cuda(args, local_rank: int, quiet: bool = False) -> dict:
+    """The reference's own kernels (oracle/_ref, compiled from its headers for sm_100a), same chain, unfused."""
+    import ctypes
+    from nemotron_infer_b200 import chain
+    path = os.path.join(ROOT, "oracle", "_ref", "libnemotron_ref.so")
+    if not os.path.exists(path):
+        return {"impl": "reference-cuda", "unavailable": "oracle/_ref/libnemotron_ref.so was not built (reference checkout absent at build time)"}
+    R = ctypes.CDLL(path)
+    torch.cuda.set_device(local_rank)
+    R.ref_set_device(local_rank)
+    T = args.tokens
+    cp = chain.ChainPass(T, f"cuda:{local_rank}", ids_dtype=torch.int64, seed=1234)
+    b = cp.buf
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    sz, fl = ctypes.c_size_t, ctypes.c_float
+    gs = chain.D_INNER // chain.N_GROUPS
+
+    def one_pass():
+        cur, other = b.hidden
+        R.ref_embedding_i64(p(b.table), p(b.ids), p(cur), sz(T), 3136, None)
+        n_m = 0
+        for i, kind in enumerate(cp.schedule):
+            if kind == "M":
+                R.ref_rmsnorm_gated_bf16(p(b.y), p(b.z), p(b.gated_w[n_m]), p(b.gated_out), sz(T), sz(chain.D_INNER), sz(gs), fl(1e-5), None)
+                n_m += 1
+            elif kind == "-":
+                R.ref_relu2_bf16(p(b.u), p(b.act), sz(T * chain.INTER), None)
+            R.ref_add_bf16(p(cur), p(b.mixer_out[i % 2]), p(other), sz(T * chain.HIDDEN), None)
+            R.ref_rmsnorm_bf16(p(other), p(b.normed), p(b.norm_w[i]), sz(T), sz(chain.HIDDEN), fl(1e-5), None)
+            cur, other = other, cur
+
+    for _ in range(3):
+        one_pass()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = max(args.steps, 1)
+    ev0.record()
+    for _ in range(steps):
+        one_pass()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / steps
+    v = T / (ms * 1e-3)
+    return {"impl": "reference-cuda", "value": round(v, 1), "unit": "tokens/s", "ms_per_step": round(ms, 4),
+            "launches_per_step": 1 + 42 * 2 + 21 + 17, "tokens": T, "steps": steps,
+            "hbm_gbs_on_fused_byte_model": round(v * chain.bytes_per_token(8) / 1e9, 1),
+            "what": "nemotron_infer's ops/reduce.cuh, ops/elementwise.cuh, ops/embedding.cuh kernels, unmodified, "
+                    "recompiled for sm_100a, legacy default stream, int64 ids, add and rmsnorm as separate launches"}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-cuda"])
+    ap.add_argument("--tokens", type=int, default=TOKENS_PER_GPU, help="tokens per GPU (weak scaling)")
+    ap.add_argument("--cpu-tokens", type=int, default=2048, help="token sample of the CPU legs")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference_cpu(args, world)), flush=True)
+        return
+    if args.impl == "reference-cuda":
+        if rank == 0:
+            print(json.dumps(run_reference_cuda(args, local_rank)), flush=True)
+        return
+
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    try:
+        out = run_b200(args, rank, world, local_rank)
+        if rank == 0 and out is not None:
+            print(json.dumps(out), flush=True)
+    finally:
+        if world > 1 and dist.is_initialized():
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,154 @@
+/*
+ * nemotron_b200.h — C ABI of libnemotron_b200.so
+ *
+ * B200 (sm_100a) replacements for the bandwidth-bound layer kernels of
+ * AIWuXin/nemotron_infer.  Each entry point names the reference host launcher
+ * it stands in for (paths are relative to the reference project root; "ops/" is
+ * nemotron_infer/csrc/include/ops/).
+ *
+ * Conventions shared by every entry point
+ *   - All pointers are DEVICE pointers owned by the caller; nothing is allocated
+ *     or freed here (the reference kernels allocate nothing either; block
+ *     workspaces come from the caller's BumpAllocator, tensor/allocator.cuh:58-175).
+ *   - `stream` is a cudaStream_t passed as void*; NULL is the legacy default
+ *     stream, which is what every reference call site passes (binding.cu:72).
+ *   - Calls are asynchronous.  The return value is an nmt_status; NMT_OK means
+ *     "validated and enqueued".  The reference returns void and never checks
+ *     anything (ops/reduce.cuh:229-244); a non-zero status here means NOTHING
+ *     was launched.
+ *   - bf16 tensors are row-major, rows contiguous (stride == cols), 16-byte
+ *     aligned, and cols % 8 == 0 — the same contract as the reference's
+ *     vectorised kernels (ops/reduce.cuh:134-135, ops/elementwise.cuh:198-201).
+ *   - rows == 0 / n == 0 is a successful no-op.
+ *   - Norm weights are fp32 (model/mlp_block.cuh:76), eps goes inside the rsqrt
+ *     after the mean (ops/reduce.cuh:174,438).
+ */
+#ifndef NEMOTRON_B200_H
+#define NEMOTRON_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum nmt_status {
+    NMT_OK = 0,
+    NMT_ERR_NULL = 1,        /* a required pointer is NULL                        */
+    NMT_ERR_ALIGN = 2,       /* a pointer is not aligned as the contract requires */
+    NMT_ERR_SHAPE = 3,       /* negative size, cols % 8 != 0, bad group size ...  */
+    NMT_ERR_LAUNCH = 4,      /* the CUDA runtime refused the launch               */
+    NMT_ERR_UNSUPPORTED = 5  /* shape outside what the kernels cover              */
+} nmt_status;
+
+/* Library identity and status text. */
+const char* nmt_version(void);
+const char* nmt_status_string(int status);
+/* Last CUDA runtime error text recorded by a failed launch on this thread. */
+const char* nmt_last_cuda_error(void);
+
+/* Makes `device` current for this library's CUDA runtime instance (the library
+ * links the static runtime, so a host that selected its device through another
+ * runtime instance should tell this one too). */
+int nmt_set_device(int device);
+/* cudaDeviceSynchronize(); replaces binding.cu:62 `sync()`. */
+int nmt_device_synchronize(void);
+
+/* ---- RMSNorm ------------------------------------------------------------- */
+
+/* y = x * rsqrt(mean(x^2) + eps) * w, fp32.
+ * Replaces nemotron::ops::rmsnorm_fp32 (ops/reduce.cuh:113-128).
+ * fp32 pointers need 4-byte alignment only; any cols >= 1. */
+int nmt_rmsnorm_f32(const float* x, float* y, const float* w,
+                    int64_t rows, int64_t cols, float eps, void* stream);
+
+/* Same, bf16 in/out, fp32 accumulation, fp32 weight.
+ * Replaces nemotron::ops::rmsnorm_bf16 (ops/reduce.cuh:229-244), which the
+ * pybind entry `rmsnorm` calls with cols = 3136 (binding.cu:71-73).
+ * y may alias x. */
+int nmt_rmsnorm_bf16(const void* x, void* y, const float* w,
+                     int64_t rows, int64_t cols, float eps, void* stream);
+
+/* Fused residual add + RMSNorm:
+ *     out_res = bf16(x + r)
+ *     out     = bf16((out_res * rsqrt(mean(out_res^2) + eps)) * w)
+ * Replaces the pair elementwise_ops_bf16<kElementwiseAdd> (ops/elementwise.cuh:
+ * 374-419, Add at :241-245) at the tail of one block (model/mlp_block.cuh:104,
+ * model/mamba_block.cuh:224, model/attention_block.cuh:210) followed by
+ * rmsnorm_bf16 at the head of the next (model/mlp_block.cuh:98,
+ * model/mamba_block.cuh:183, model/attention_block.cuh:196, binding.cu:72).
+ * The sum of squares is taken over the bf16-ROUNDED sum, exactly what the
+ * unfused pair computes.  out_res may alias x or r; out must not alias an input. */
+int nmt_add_rmsnorm_bf16(const void* x, const void* r, const float* w,
+                         void* out_res, void* out,
+                         int64_t rows, int64_t cols, float eps, void* stream);
+
+/* ---- Mamba-2 gated RMSNorm ------------------------------------------------ */
+
+/* g = y * silu(z); per group of `group_size` channels:
+ *     out = (g * rsqrt(mean_group(g^2) + eps)) * w
+ * Replaces nemotron::ops::rmsnorm_gated_bf16<Group> (ops/reduce.cuh:510-527;
+ * called at model/mamba_block.cuh:217 with cols = 7680, group_size = 960).
+ * The reference's argument order is (in, out, w, gate, ...); here y = in and
+ * z = gate.  cols % group_size == 0.  out may alias y or z. */
+int nmt_rmsnorm_gated_bf16(const void* y, const void* z, const float* w, void* out,
+                           int64_t rows, int64_t cols, int64_t group_size,
+                           float eps, void* stream);
+
+/* fp32 twin; replaces nemotron::ops::rmsnorm_gated_fp32<Group>
+ * (ops/reduce.cuh:360-377). */
+int nmt_rmsnorm_gated_f32(const float* y, const float* z, const float* w, float* out,
+                          int64_t rows, int64_t cols, int64_t group_size,
+                          float eps, void* stream);
+
+/* ---- Elementwise ----------------------------------------------------------- */
+
+/* out = max(u, 0)^2, bf16 (the fp32 square rounded to nearest even; NaN
+ * propagates).  Replaces elementwise_ops_bf16<kElementwiseRelu2>
+ * (ops/elementwise.cuh:256-272, launcher :374-419; caller model/mlp_block.cuh:
+ * 100).  n = number of elements, n % 8 == 0.  out may alias u. */
+int nmt_relu2_bf16(const void* u, void* out, int64_t n, void* stream);
+
+/* fp32 twin of relu2; replaces elementwise_ops_fp32<kElementwiseRelu2>
+ * (ops/elementwise.cuh:100-104,177-195).  Any n (scalar tail handled). */
+int nmt_relu2_f32(const float* u, float* out, int64_t n, void* stream);
+
+/* out = a + b, bf16 with a single rounding.  Replaces
+ * elementwise_ops_bf16<kElementwiseAdd> (ops/elementwise.cuh:241-245).
+ * n % 8 == 0.  out may alias a or b. */
+int nmt_add_bf16(const void* a, const void* b, void* out, int64_t n, void* stream);
+
+/* fp32 twin of add; replaces elementwise_ops_fp32<kElementwiseAdd>
+ * (ops/elementwise.cuh:85-89,177-195).  Any n. */
+int nmt_add_f32(const float* a, const float* b, float* out, int64_t n, void* stream);
+
+/* ---- Token-embedding gather ------------------------------------------------ */
+
+/* out[i, :] = table[ids[i], :], a bit-exact row copy.
+ * Replaces nemotron::ops::embedding_lookup<Hidden> (ops/embedding.cuh:53-66;
+ * bound as `embedding` at binding.cu:65-68 with int64 ids, hidden = 3136).
+ * hidden % 8 == 0.  The reference never range-checks an id; here an id outside
+ * [0, vocab) is never dereferenced: its output row is zero-filled and, when
+ * err_flag != NULL, *err_flag (device int32) is set to 1.  Pass vocab <= 0 to
+ * disable the check (the reference's behaviour). */
+int nmt_embedding_bf16_i64(const void* table, const int64_t* ids, void* out,
+                           int64_t num_tokens, int64_t hidden, int64_t vocab,
+                           int32_t* err_flag, void* stream);
+int nmt_embedding_bf16_i32(const void* table, const int32_t* ids, void* out,
+                           int64_t num_tokens, int64_t hidden, int64_t vocab,
+                           int32_t* err_flag, void* stream);
+
+/* ---- Test and tuning hooks -------------------------------------------------- */
+
+/* Selects a kernel variant / launch shape by name (for measurement sweeps).
+ * Unknown keys return NMT_ERR_UNSUPPORTED.  Not needed in normal use: the
+ * defaults are the measured-best settings. */
+int nmt_tune_set(const char* key, int value);
+int nmt_tune_get(const char* key, int* value);
+/* Number of kernel launches this library has enqueued since load (all threads). */
+int64_t nmt_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NEMOTRON_B200_H */

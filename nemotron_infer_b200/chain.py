@@ -1,0 +1,137 @@
+"""One forward pass worth of the hot-path ops, in model order, on one GPU's shard of the tokens.
+
+Per pass and per token the reference engine runs (engine.py:254-272 with the
+block bodies in model/{mamba,attention,mlp}_block.cuh): one embedding gather,
+42 pre-norm RMSNorms each preceded by the previous block's residual add, 21
+gated RMSNorms inside the Mamba-2 blocks and 17 relu^2 inside the MLP blocks.
+With the add fused into the norm that follows it this is 1 + 42 + 21 + 17 = 81
+launches.  The GEMMs, scans and attention between them are not part of this
+library; their outputs are stood in for by resident synthetic tensors (the
+"mixer outputs"), which is also how the ops see them in the engine: as bf16
+tensors already in device memory.
+
+Every op is independent per token row, so N GPUs each run the same chain on
+their own rows with no exchange: `shard_range` gives rank k its rows.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+
+HIDDEN = 3136
+D_INNER = 6144            # width of the gated RMSNorm in the benchmark configuration
+N_GROUPS = 8
+INTER = 12544
+VOCAB = 131072
+N_LAYERS = 42
+
+
+def layer_schedule() -> str:
+    """42 layers: 'M' Mamba-2 (21), '-' MLP (17), '*' attention (4), interleaved like a hybrid stack."""
+    pat = "M-M-M-M-M*" * 4 + "M-"
+    assert len(pat) == N_LAYERS and pat.count("M") == 21 and pat.count("-") == 17 and pat.count("*") == 4
+    return pat
+
+
+def shard_range(total_rows: int, rank: int, world: int) -> tuple[int, int]:
+    """Rows [lo, hi) that rank `rank` of `world` owns: contiguous, balanced to within one row."""
+    if world < 1 or not (0 <= rank < world) or total_rows < 0:
+        raise ValueError("bad shard request")
+    return (rank * total_rows) // world, ((rank + 1) * total_rows) // world
+
+
+def bytes_per_token(ids_bytes: int = 4) -> int:
+    """Algorithmic HBM bytes one token costs per pass (each activation byte crosses HBM once)."""
+    gather = 2 * HIDDEN * 2 + ids_bytes
+    return gather + 42 * (4 * HIDDEN * 2) + 21 * (3 * D_INNER * 2) + 17 * (2 * INTER * 2)
+
+
+@dataclass
+class ChainBuffers:
+    table: torch.Tensor
+    ids: torch.Tensor
+    hidden: list            # two [T, HIDDEN] ping-pong buffers (engine.py:70)
+    normed: torch.Tensor
+    mixer_out: list         # stand-ins for the blocks' GEMM outputs, rotated
+    y: torch.Tensor
+    z: torch.Tensor
+    gated_out: torch.Tensor
+    u: torch.Tensor
+    act: torch.Tensor
+    norm_w: torch.Tensor    # [42, HIDDEN] fp32
+    gated_w: torch.Tensor   # [21, D_INNER] fp32
+    err_flag: torch.Tensor
+
+
+class ChainPass:
+    """Holds the resident tensors of one shard and enqueues the 81-launch pass."""
+
+    def __init__(self, tokens: int, device, ids_dtype=torch.int32, seed: int = 0, mixer_sets: int = 2,
+                 vocab: int = VOCAB, init: dict | None = None):
+        self.tokens = int(tokens)
+        self.device = torch.device(device)
+        self.schedule = layer_schedule()
+        T, dev, bf = self.tokens, self.device, torch.bfloat16
+        if init is None:
+            g = torch.Generator(device=dev)
+            g.manual_seed(seed)
+            rn = lambda *s: torch.randn(*s, generator=g, device=dev, dtype=torch.float32)  # noqa: E731
+            table = torch.empty(vocab, HIDDEN, device=dev, dtype=bf)
+            step = 8192
+            for lo in range(0, vocab, step):      # chunked: keeps the fp32 temporary small
+                table[lo:lo + step] = (0.02 * rn(min(step, vocab - lo), HIDDEN)).to(bf)
+            ids = torch.randint(0, vocab, (T,), generator=g, device=dev, dtype=torch.int64).to(ids_dtype)
+
+            def big(cols, scale=1.0):
+                out = torch.empty(T, cols, device=dev, dtype=bf)
+                rows = max(1, (1 << 26) // cols)
+                for lo in range(0, T, rows):
+                    out[lo:lo + rows] = (scale * rn(min(rows, T - lo), cols)).to(bf)
+                return out
+            init = dict(table=table, ids=ids, mixer_out=[big(HIDDEN) for _ in range(mixer_sets)],
+                        y=big(D_INNER), z=big(D_INNER), u=big(INTER, 2.0),
+                        norm_w=1.0 + 0.1 * rn(N_LAYERS, HIDDEN), gated_w=1.0 + 0.1 * rn(21, D_INNER))
+        mk = lambda cols: torch.empty(T, cols, device=dev, dtype=bf)  # noqa: E731
+        self.buf = ChainBuffers(
+            table=init["table"].to(dev), ids=init["ids"].to(dev),
+            hidden=[mk(HIDDEN), mk(HIDDEN)], normed=mk(HIDDEN),
+            mixer_out=[t.to(dev) for t in init["mixer_out"]],
+            y=init["y"].to(dev), z=init["z"].to(dev), gated_out=mk(D_INNER),
+            u=init["u"].to(dev), act=mk(INTER),
+            norm_w=init["norm_w"].to(dev).contiguous(), gated_w=init["gated_w"].to(dev).contiguous(),
+            err_flag=torch.zeros(1, device=dev, dtype=torch.int32))
+        self.launches_per_pass = 1 + 42 + 21 + 17
+        self._host_ids = None
+        self._host_out = None
+
+    def run(self) -> torch.Tensor:
+        """Enqueues one pass on torch's current stream; returns the final normed hidden states [T, HIDDEN]."""
+        b = self.buf
+        cur, other = b.hidden
+        ops.embedding(b.table, b.ids, out=cur, err_flag=b.err_flag)
+        n_m = 0
+        for i, kind in enumerate(self.schedule):
+            if kind == "M":
+                ops.rmsnorm_gated(b.y, b.z, b.gated_w[n_m], D_INNER // N_GROUPS, out=b.gated_out)
+                n_m += 1
+            elif kind == "-":
+                ops.relu2(b.u, out=b.act)
+            ops.add_rmsnorm(cur, b.mixer_out[i % len(b.mixer_out)], b.norm_w[i], out_res=other, out=b.normed)
+            cur, other = other, cur
+        self.final_hidden = cur
+        return b.normed
+
+    def run_from_host(self, ids_host: torch.Tensor) -> torch.Tensor:
+        """The end-to-end call: token ids arrive in (pinned) host memory, the last token's normed hidden
+        state comes back to host memory — what the engine's prefill hands to lm_head (engine.py:241-251)."""
+        b = self.buf
+        if self._host_out is None:
+            self._host_out = torch.empty(HIDDEN, dtype=torch.bfloat16).pin_memory()
+        b.ids.copy_(ids_host, non_blocking=True)
+        normed = self.run()
+        self._host_out.copy_(normed[self.tokens - 1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._host_out

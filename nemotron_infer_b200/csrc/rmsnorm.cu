@@ -1,0 +1,230 @@
+// RMSNorm and fused residual-add + RMSNorm.
+//
+// Register variant: one warp owns one row.  A 3136-wide bf16 row is 392 16-byte
+// vectors, i.e. 13 lane slots (the last one 8 lanes wide).  All loads of a row
+// are issued before the first use, the rounded sum x+r stays in registers
+// between the sum of squares and the scaling, the reduction is five shuffles,
+// and there is no shared memory and no block barrier.  Every activation byte
+// crosses HBM once: read x, read r, write out_res, write out.
+#include "nmt_common.cuh"
+
+namespace nmt {
+
+template <int SLOTS, bool FUSE_ADD>
+__global__ void __launch_bounds__(256)
+rmsnorm_rowwarp_kernel(const uint4* x, const uint4* r,
+                       const float* __restrict__ w, uint4* out_res, uint4* out,
+                       int64_t rows, int nv, float inv_cols, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int warps_per_cta = blockDim.x >> 5;
+    const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * warps_per_cta;
+
+    for (int64_t row = warp0; row < rows; row += nwarps) {
+        const uint4* xr = x + row * nv;
+        const uint4* rr = FUSE_ADD ? r + row * nv : nullptr;
+        uint4 a[SLOTS], b[SLOTS];
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int v = s * 32 + lane;
+            if (v < nv) {
+                a[s] = ld_stream(xr + v);
+                if (FUSE_ADD) b[s] = ld_stream(rr + v);
+            } else {
+                a[s] = make_uint4(0, 0, 0, 0);
+                if (FUSE_ADD) b[s] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            float f[8];
+            unpack8(a[s], f);
+            if (FUSE_ADD) {
+                float g[8];
+                unpack8(b[s], g);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] += g[k];
+                // Round the residual stream to bf16 first: the norm must see what the
+                // next block would read back from memory.
+                a[s] = pack8(f);
+                unpack8(a[s], f);
+                const int v = s * 32 + lane;
+                if (v < nv) st_stream(out_res + row * nv + v, a[s]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss = fmaf(f[k], f[k], ss);
+        }
+        ss = warp_sum(ss);
+        const float rstd = rsqrtf(ss * inv_cols + eps);
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int v = s * 32 + lane;
+            if (v < nv) {
+                float f[8];
+                unpack8(a[s], f);
+                const float4 w0 = ld_weight4(w + v * 8);
+                const float4 w1 = ld_weight4(w + v * 8 + 4);
+                f[0] = (f[0] * rstd) * w0.x; f[1] = (f[1] * rstd) * w0.y;
+                f[2] = (f[2] * rstd) * w0.z; f[3] = (f[3] * rstd) * w0.w;
+                f[4] = (f[4] * rstd) * w1.x; f[5] = (f[5] * rstd) * w1.y;
+                f[6] = (f[6] * rstd) * w1.z; f[7] = (f[7] * rstd) * w1.w;
+                st_stream(out + row * nv + v, pack8(f));
+            }
+        }
+    }
+}
+
+// Any width: one CTA per row, two passes.  The second pass re-reads what the
+// first pass of the same thread touched (out_res when fused, else x), so the
+// re-read is served by L2 for all but pathological widths.
+template <bool FUSE_ADD>
+__global__ void __launch_bounds__(256)
+rmsnorm_rowcta_kernel(const uint4* x, const uint4* r,
+                      const float* __restrict__ w, uint4* out_res, uint4* out,
+                      int64_t rows, int64_t nv, float inv_cols, float eps) {
+    __shared__ float s_part[8];
+    __shared__ float s_total;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint4* xr = x + row * nv;
+        float ss = 0.f;
+        for (int64_t v = threadIdx.x; v < nv; v += blockDim.x) {
+            uint4 a = ld_stream(xr + v);
+            float f[8];
+            unpack8(a, f);
+            if (FUSE_ADD) {
+                float g[8];
+                unpack8(ld_stream(r + row * nv + v), g);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] += g[k];
+                a = pack8(f);
+                unpack8(a, f);
+                out_res[row * nv + v] = a;
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss = fmaf(f[k], f[k], ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) s_part[wid] = ss;
+        __syncthreads();
+        if (wid == 0) {
+            float t = lane < (blockDim.x >> 5) ? s_part[lane] : 0.f;
+            t = warp_sum(t);
+            if (lane == 0) s_total = t;
+        }
+        __syncthreads();
+        const float rstd = rsqrtf(s_total * inv_cols + eps);
+        const uint4* src = FUSE_ADD ? out_res + row * nv : xr;
+        for (int64_t v = threadIdx.x; v < nv; v += blockDim.x) {
+            float f[8];
+            unpack8(src[v], f);
+            const float4 w0 = ld_weight4(w + v * 8);
+            const float4 w1 = ld_weight4(w + v * 8 + 4);
+            f[0] = (f[0] * rstd) * w0.x; f[1] = (f[1] * rstd) * w0.y;
+            f[2] = (f[2] * rstd) * w0.z; f[3] = (f[3] * rstd) * w0.w;
+            f[4] = (f[4] * rstd) * w1.x; f[5] = (f[5] * rstd) * w1.y;
+            f[6] = (f[6] * rstd) * w1.z; f[7] = (f[7] * rstd) * w1.w;
+            out[row * nv + v] = pack8(f);
+        }
+        __syncthreads();   // s_part / s_total are reused by the next row
+    }
+}
+
+// fp32 twin (parity only): one CTA per row, scalar, two passes.
+__global__ void __launch_bounds__(256)
+rmsnorm_f32_kernel(const float* __restrict__ x, float* y, const float* __restrict__ w,
+                   int64_t rows, int64_t cols, float eps) {
+    __shared__ float s_part[8];
+    __shared__ float s_total;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float* xr = x + row * cols;
+        float ss = 0.f;
+        for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) { const float v = xr[c]; ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        if (lane == 0) s_part[wid] = ss;
+        __syncthreads();
+        if (wid == 0) {
+            float t = lane < (blockDim.x >> 5) ? s_part[lane] : 0.f;
+            t = warp_sum(t);
+            if (lane == 0) s_total = t;
+        }
+        __syncthreads();
+        const float rstd = rsqrtf(s_total / static_cast<float>(cols) + eps);
+        for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) y[row * cols + c] = (xr[c] * rstd) * w[c];
+        __syncthreads();
+    }
+}
+
+template <bool FUSE_ADD>
+static int launch_norm_bf16(const void* x, const void* r, const float* w, void* out_res, void* out,
+                            int64_t rows, int64_t cols, float eps, cudaStream_t st) {
+    const int64_t nv = cols / 8;
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    auto X = static_cast<const uint4*>(x);
+    auto R = static_cast<const uint4*>(r);
+    auto OR = static_cast<uint4*>(out_res);
+    auto O = static_cast<uint4*>(out);
+
+    if (nv > 16 * 32) {
+        const int grid = grid_for(rows, 1, kSmCount * 16);
+        rmsnorm_rowcta_kernel<FUSE_ADD><<<grid, 256, 0, st>>>(X, R, w, OR, O, rows, nv, inv_cols, eps);
+        return finish_launch(1);
+    }
+    int block = tune("norm.block", 256);
+    block = block > 256 ? 256 : (block + 31) / 32 * 32;
+    const int wpc = block / 32;
+    const int per_sm = tune("norm.ctas_per_sm", 0);
+    const int grid = grid_for(rows, wpc, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);
+    const int slots = static_cast<int>((nv + 31) / 32);
+#define NMT_NORM_CASE(S)                                                                           \
+    rmsnorm_rowwarp_kernel<S, FUSE_ADD><<<grid, block, 0, st>>>(X, R, w, OR, O, rows, (int)nv, inv_cols, eps)
+    if (slots <= 2) NMT_NORM_CASE(2);
+    else if (slots <= 4) NMT_NORM_CASE(4);
+    else if (slots <= 8) NMT_NORM_CASE(8);
+    else if (slots <= 13) NMT_NORM_CASE(13);
+    else NMT_NORM_CASE(16);
+#undef NMT_NORM_CASE
+    return finish_launch(1);
+}
+
+static int check_norm_args(const void* x, const void* y, const float* w, int64_t rows, int64_t cols) {
+    if (rows < 0 || cols <= 0 || (cols % 8) != 0) return NMT_ERR_SHAPE;
+    if (rows == 0) return NMT_OK;
+    if (!x || !y || !w) return NMT_ERR_NULL;
+    if (!aligned16(x) || !aligned16(y) || !aligned16(w)) return NMT_ERR_ALIGN;
+    return NMT_OK;
+}
+
+}  // namespace nmt
+
+extern "C" {
+
+int nmt_rmsnorm_f32(const float* x, float* y, const float* w, int64_t rows, int64_t cols, float eps, void* stream) {
+    if (rows < 0 || cols <= 0) return NMT_ERR_SHAPE;
+    if (rows == 0) return NMT_OK;
+    if (!x || !y || !w) return NMT_ERR_NULL;
+    if (!nmt::aligned4(x) || !nmt::aligned4(y) || !nmt::aligned4(w)) return NMT_ERR_ALIGN;
+    const int grid = nmt::grid_for(rows, 1, nmt::kSmCount * 8);
+    nmt::rmsnorm_f32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, w, rows, cols, eps);
+    return nmt::finish_launch(1);
+}
+
+int nmt_rmsnorm_bf16(const void* x, void* y, const float* w, int64_t rows, int64_t cols, float eps, void* stream) {
+    int s = nmt::check_norm_args(x, y, w, rows, cols);
+    if (s != NMT_OK || rows == 0) return s;
+    return nmt::launch_norm_bf16<false>(x, nullptr, w, nullptr, y, rows, cols, eps, static_cast<cudaStream_t>(stream));
+}
+
+int nmt_add_rmsnorm_bf16(const void* x, const void* r, const float* w, void* out_res, void* out,
+                         int64_t rows, int64_t cols, float eps, void* stream) {
+    int s = nmt::check_norm_args(x, out, w, rows, cols);
+    if (s != NMT_OK || rows == 0) return s;
+    if (!r || !out_res) return NMT_ERR_NULL;
+    if (!nmt::aligned16(r) || !nmt::aligned16(out_res)) return NMT_ERR_ALIGN;
+    if (out == x || out == r || out == out_res) return NMT_ERR_SHAPE;
+    return nmt::launch_norm_bf16<true>(x, r, w, out_res, out, rows, cols, eps, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

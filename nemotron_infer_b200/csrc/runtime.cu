@@ -1,0 +1,115 @@
+// Library identity, status text, device selection and the tuning-knob table.
+#include <cstring>
+#include <cstdio>
+
+#include "nmt_common.cuh"
+
+namespace nmt {
+
+std::atomic<int64_t> g_launches{0};
+static thread_local char t_cuda_err[256] = "";
+
+int finish_launch(int n_kernels) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        snprintf(t_cuda_err, sizeof(t_cuda_err), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+        return NMT_ERR_LAUNCH;
+    }
+    g_launches.fetch_add(n_kernels, std::memory_order_relaxed);
+    return NMT_OK;
+}
+
+// Knobs are plain ints read at launch time.  0 means "let the launcher decide".
+struct Knob { const char* key; std::atomic<int> value; };
+static Knob g_knobs[] = {
+    // add_rmsnorm / rmsnorm (bf16)
+    {"norm.variant", {0}},        // 0 = auto, 1 = warp-per-row registers, 2 = TMA-staged tiles
+    {"norm.block", {0}},          // threads per CTA for the warp-per-row kernel
+    {"norm.ctas_per_sm", {0}},    // >0: persistent grid of 148*k CTAs; 0: one pass, grid = rows/warps
+    {"norm.tma_rows", {0}},       // rows per TMA stage
+    {"norm.tma_stages", {0}},
+    // gated rmsnorm (bf16)
+    {"gated.variant", {0}},       // 0 = auto, 1 = warp-per-group registers, 2 = TMA-staged rows
+    {"gated.block", {0}},
+    {"gated.ctas_per_sm", {0}},
+    {"gated.rows_per_iter", {0}},
+    {"gated.tma_stages", {0}},
+    // relu2 / add (bf16)
+    {"ew.variant", {0}},          // 0 = auto, 1 = register streaming, 2 = TMA-staged chunks
+    {"ew.block", {0}},
+    {"ew.unroll", {0}},
+    {"ew.ctas_per_sm", {0}},
+    {"ew.tma_chunk", {0}},        // bytes per TMA stage
+    {"ew.tma_stages", {0}},
+    // embedding gather
+    {"emb.variant", {0}},         // 0 = auto, 1 = warp-per-row registers, 2 = TMA row relay
+    {"emb.block", {0}},
+    {"emb.ctas_per_sm", {0}},
+    {"emb.tma_rows", {0}},
+    {"emb.tma_stages", {0}},
+};
+static Knob* find_knob(const char* key) {
+    if (!key) return nullptr;
+    for (auto& k : g_knobs) if (std::strcmp(k.key, key) == 0) return &k;
+    return nullptr;
+}
+int tune(const char* key, int dflt) {
+    Knob* k = find_knob(key);
+    if (!k) return dflt;
+    int v = k->value.load(std::memory_order_relaxed);
+    return v > 0 ? v : dflt;
+}
+
+}  // namespace nmt
+
+extern "C" {
+
+const char* nmt_version(void) { return "nemotron_b200 0.1 (sm_100a)"; }
+
+const char* nmt_status_string(int s) {
+    switch (s) {
+        case NMT_OK: return "ok";
+        case NMT_ERR_NULL: return "null pointer";
+        case NMT_ERR_ALIGN: return "pointer not aligned to the contract (16 bytes for bf16 tensors, 4 for fp32)";
+        case NMT_ERR_SHAPE: return "bad shape (negative size, cols % 8 != 0, or group size does not divide cols)";
+        case NMT_ERR_LAUNCH: return "CUDA launch failed (see nmt_last_cuda_error)";
+        case NMT_ERR_UNSUPPORTED: return "unsupported shape or unknown tuning key";
+        default: return "unknown status";
+    }
+}
+
+const char* nmt_last_cuda_error(void) { return nmt::t_cuda_err; }
+
+int nmt_set_device(int device) {
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) {
+        snprintf(nmt::t_cuda_err, sizeof(nmt::t_cuda_err), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+        return NMT_ERR_LAUNCH;
+    }
+    return NMT_OK;
+}
+
+int nmt_device_synchronize(void) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+        snprintf(nmt::t_cuda_err, sizeof(nmt::t_cuda_err), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
+        return NMT_ERR_LAUNCH;
+    }
+    return NMT_OK;
+}
+
+int nmt_tune_set(const char* key, int value) {
+    nmt::Knob* k = nmt::find_knob(key);
+    if (!k) return NMT_ERR_UNSUPPORTED;
+    k->value.store(value, std::memory_order_relaxed);
+    return NMT_OK;
+}
+int nmt_tune_get(const char* key, int* value) {
+    nmt::Knob* k = nmt::find_knob(key);
+    if (!k || !value) return NMT_ERR_UNSUPPORTED;
+    *value = k->value.load(std::memory_order_relaxed);
+    return NMT_OK;
+}
+int64_t nmt_launch_count(void) { return nmt::g_launches.load(std::memory_order_relaxed); }
+
+}  // extern "C"

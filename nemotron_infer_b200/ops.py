@@ -1,0 +1,160 @@
+"""Tensor-level operators over the C-ABI library (torch tensors in, torch tensors out).
+
+torch is used for device memory and streams only; every operator validates its
+arguments, takes `data_ptr()` of each tensor (the same hand-off the reference's
+engine does, engine.py:40-42) and calls libnemotron_b200.so on torch's current
+stream.  There is no eager/PyTorch fallback: a CPU tensor or a missing library
+raises.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import NemotronB200Error  # noqa: F401  (re-exported)
+
+EPS = 1e-5
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if not t.is_cuda:
+            raise ValueError("nemotron_infer_b200 operators run on CUDA tensors only (no CPU fallback)")
+        if not t.is_contiguous():
+            raise ValueError("tensors must be contiguous (row stride == cols)")
+    dev = ts[0].device
+    if any(t.device != dev for t in ts):
+        raise ValueError("all tensors must live on the same device")
+
+
+def _rows_cols(t: torch.Tensor) -> tuple[int, int]:
+    cols = t.shape[-1] if t.dim() else 1
+    return (t.numel() // cols if cols else 0), cols
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = EPS, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x * rsqrt(mean(x^2) + eps) * w over the last dim; bf16 or fp32 x, fp32 w."""
+    out = torch.empty_like(x) if out is None else out
+    _dev(x, w, out)
+    if w.dtype != torch.float32 or out.dtype != x.dtype or out.shape != x.shape:
+        raise ValueError("w must be fp32 and out must match x")
+    rows, cols = _rows_cols(x)
+    if w.numel() != cols:
+        raise ValueError("w must have one entry per column")
+    lib = _lib.load()
+    if x.dtype == torch.bfloat16:
+        st = lib.nmt_rmsnorm_bf16(x.data_ptr(), out.data_ptr(), w.data_ptr(), rows, cols, eps, _stream())
+    elif x.dtype == torch.float32:
+        st = lib.nmt_rmsnorm_f32(x.data_ptr(), out.data_ptr(), w.data_ptr(), rows, cols, eps, _stream())
+    else:
+        raise ValueError("x must be bf16 or fp32")
+    _lib.check(st, "rmsnorm")
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, r: torch.Tensor, w: torch.Tensor, eps: float = EPS,
+                out_res: torch.Tensor | None = None, out: torch.Tensor | None = None):
+    """(out_res, out) with out_res = bf16(x + r) and out = rmsnorm(out_res) * w, in one pass over HBM."""
+    out_res = torch.empty_like(x) if out_res is None else out_res
+    out = torch.empty_like(x) if out is None else out
+    _dev(x, r, w, out_res, out)
+    if x.dtype != torch.bfloat16 or r.dtype != x.dtype or out.dtype != x.dtype or out_res.dtype != x.dtype:
+        raise ValueError("x, r, out_res and out must be bf16")
+    if w.dtype != torch.float32:
+        raise ValueError("w must be fp32")
+    if not (x.shape == r.shape == out.shape == out_res.shape):
+        raise ValueError("x, r, out_res and out must have the same shape")
+    rows, cols = _rows_cols(x)
+    if w.numel() != cols:
+        raise ValueError("w must have one entry per column")
+    st = _lib.load().nmt_add_rmsnorm_bf16(x.data_ptr(), r.data_ptr(), w.data_ptr(), out_res.data_ptr(),
+                                          out.data_ptr(), rows, cols, eps, _stream())
+    _lib.check(st, "add_rmsnorm")
+    return out_res, out
+
+
+def rmsnorm_gated(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, group_size: int, eps: float = EPS,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = (g * rsqrt(mean_group(g^2) + eps)) * w with g = y * silu(z); bf16 or fp32."""
+    out = torch.empty_like(y) if out is None else out
+    _dev(y, z, w, out)
+    if z.dtype != y.dtype or out.dtype != y.dtype or w.dtype != torch.float32:
+        raise ValueError("y, z and out must share a dtype and w must be fp32")
+    if not (y.shape == z.shape == out.shape):
+        raise ValueError("y, z and out must have the same shape")
+    rows, cols = _rows_cols(y)
+    if w.numel() != cols:
+        raise ValueError("w must have one entry per column")
+    lib = _lib.load()
+    fn = {torch.bfloat16: lib.nmt_rmsnorm_gated_bf16, torch.float32: lib.nmt_rmsnorm_gated_f32}.get(y.dtype)
+    if fn is None:
+        raise ValueError("y must be bf16 or fp32")
+    _lib.check(fn(y.data_ptr(), z.data_ptr(), w.data_ptr(), out.data_ptr(), rows, cols, int(group_size), eps,
+                  _stream()), "rmsnorm_gated")
+    return out
+
+
+def relu2(u: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = relu(u)^2; bf16 or fp32."""
+    out = torch.empty_like(u) if out is None else out
+    _dev(u, out)
+    if out.dtype != u.dtype or out.shape != u.shape:
+        raise ValueError("out must match u")
+    lib = _lib.load()
+    fn = {torch.bfloat16: lib.nmt_relu2_bf16, torch.float32: lib.nmt_relu2_f32}.get(u.dtype)
+    if fn is None:
+        raise ValueError("u must be bf16 or fp32")
+    _lib.check(fn(u.data_ptr(), out.data_ptr(), u.numel(), _stream()), "relu2")
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = a + b; bf16 (single rounding) or fp32."""
+    out = torch.empty_like(a) if out is None else out
+    _dev(a, b, out)
+    if b.dtype != a.dtype or out.dtype != a.dtype or not (a.shape == b.shape == out.shape):
+        raise ValueError("a, b and out must match")
+    lib = _lib.load()
+    fn = {torch.bfloat16: lib.nmt_add_bf16, torch.float32: lib.nmt_add_f32}.get(a.dtype)
+    if fn is None:
+        raise ValueError("a must be bf16 or fp32")
+    _lib.check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), _stream()), "add")
+    return out
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None,
+              err_flag: torch.Tensor | None = None, check_range: bool = True) -> torch.Tensor:
+    """out[i, :] = table[ids[i], :]; bf16 table, int32 or int64 ids.  With check_range, an id outside
+    [0, vocab) zero-fills its row and sets err_flag (device int32[1]) instead of reading out of bounds."""
+    vocab, hidden = table.shape
+    out = torch.empty((ids.numel(), hidden), dtype=table.dtype, device=table.device) if out is None else out
+    _dev(table, ids, out)
+    if table.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise ValueError("table and out must be bf16")
+    if out.numel() != ids.numel() * hidden:
+        raise ValueError("out must hold ids.numel() rows of table width")
+    lib = _lib.load()
+    fn = {torch.int64: lib.nmt_embedding_bf16_i64, torch.int32: lib.nmt_embedding_bf16_i32}.get(ids.dtype)
+    if fn is None:
+        raise ValueError("ids must be int32 or int64")
+    if err_flag is not None:
+        _dev(err_flag)
+        if err_flag.dtype != torch.int32:
+            raise ValueError("err_flag must be int32")
+    _lib.check(fn(table.data_ptr(), ids.data_ptr(), out.data_ptr(), ids.numel(), hidden,
+                  vocab if check_range else 0, err_flag.data_ptr() if err_flag is not None else None, _stream()),
+               "embedding")
+    return out
+
+
+def tune(key: str, value: int) -> None:
+    """Sets a launch-shape / variant knob (see nmt_tune_set in include/nemotron_b200.h)."""
+    _lib.check(_lib.load().nmt_tune_set(key.encode(), int(value)), f"tune({key})")
+
+
+def launch_count() -> int:
+    return int(_lib.load().nmt_launch_count())

@@ -1,0 +1,100 @@
+// TEST INFRASTRUCTURE — extern "C" doors onto the reference's OWN host launchers,
+// compiled from the reference's headers where they lie (nothing is copied): the
+// Makefile passes -I <reference>/nemotron_infer/csrc/include.  The resulting
+// library is used by the GPU parity tests as a second checker and by bench.py to
+// time "the reference kernels recompiled for sm_100a" beside the new kernels.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+
+#include "tensor/tensor.h"
+#include "ops/reduce.cuh"        // rmsnorm_{fp32,bf16}, rmsnorm_gated_{fp32,bf16}<Group>
+#include "ops/elementwise.cuh"   // elementwise_ops_{fp32,bf16}<Op>
+#include "ops/embedding.cuh"     // embedding_lookup<Hidden>
+
+using namespace nemotron::ops;
+using bf16 = __nv_bfloat16;
+
+#define REF_API extern "C" __attribute__((visibility("default")))
+
+static int last() { return static_cast<int>(cudaGetLastError()); }
+
+REF_API int ref_rmsnorm_fp32(const float* x, float* y, const float* w, size_t rows, size_t cols, float eps, void* st) {
+    rmsnorm_fp32(x, y, w, rows, cols, eps, static_cast<cudaStream_t>(st));
+    return last();
+}
+REF_API int ref_rmsnorm_bf16(const void* x, void* y, const float* w, size_t rows, size_t cols, float eps, void* st) {
+    rmsnorm_bf16(static_cast<const bf16*>(x), static_cast<bf16*>(y), w, rows, cols, eps, static_cast<cudaStream_t>(st));
+    return last();
+}
+
+template <int G>
+static void gated_bf16(const void* y, void* out, const float* w, const void* z, size_t rows, size_t cols, size_t gs,
+                       float eps, cudaStream_t st) {
+    rmsnorm_gated_bf16<G>(static_cast<const bf16*>(y), static_cast<bf16*>(out), w, static_cast<const bf16*>(z),
+                          rows, cols, gs, eps, st);
+}
+// Group is a template parameter in the reference (binding.cu uses G = 8); the door covers the counts the tests use.
+REF_API int ref_rmsnorm_gated_bf16(const void* y, const void* z, const float* w, void* out, size_t rows, size_t cols,
+                                   size_t gs, float eps, void* stv) {
+    cudaStream_t st = static_cast<cudaStream_t>(stv);
+    switch (cols / gs) {
+        case 1: gated_bf16<1>(y, out, w, z, rows, cols, gs, eps, st); break;
+        case 2: gated_bf16<2>(y, out, w, z, rows, cols, gs, eps, st); break;
+        case 3: gated_bf16<3>(y, out, w, z, rows, cols, gs, eps, st); break;
+        case 4: gated_bf16<4>(y, out, w, z, rows, cols, gs, eps, st); break;
+        case 8: gated_bf16<8>(y, out, w, z, rows, cols, gs, eps, st); break;
+        default: return -1;
+    }
+    return last();
+}
+REF_API int ref_rmsnorm_gated_fp32(const float* y, const float* z, const float* w, float* out, size_t rows, size_t cols,
+                                   size_t gs, float eps, void* stv) {
+    cudaStream_t st = static_cast<cudaStream_t>(stv);
+    switch (cols / gs) {
+        case 1: rmsnorm_gated_fp32<1>(y, out, w, z, rows, cols, gs, eps, st); break;
+        case 2: rmsnorm_gated_fp32<2>(y, out, w, z, rows, cols, gs, eps, st); break;
+        case 3: rmsnorm_gated_fp32<3>(y, out, w, z, rows, cols, gs, eps, st); break;
+        case 4: rmsnorm_gated_fp32<4>(y, out, w, z, rows, cols, gs, eps, st); break;
+        case 8: rmsnorm_gated_fp32<8>(y, out, w, z, rows, cols, gs, eps, st); break;
+        default: return -1;
+    }
+    return last();
+}
+
+REF_API int ref_add_bf16(const void* a, const void* b, void* out, size_t n, void* st) {
+    elementwise_ops_bf16<kElementwiseAdd>(static_cast<const bf16*>(a), static_cast<const bf16*>(b),
+                                          static_cast<bf16*>(out), n, 1.f, nullptr, 0.f, 1.f,
+                                          static_cast<cudaStream_t>(st));
+    return last();
+}
+REF_API int ref_relu2_bf16(const void* u, void* out, size_t n, void* st) {
+    // Same call shape as model/mlp_block.cuh:100 (in1 = in0).
+    elementwise_ops_bf16<kElementwiseRelu2>(static_cast<const bf16*>(u), static_cast<const bf16*>(u),
+                                            static_cast<bf16*>(out), n, 1.f, nullptr, 0.f, 1.f,
+                                            static_cast<cudaStream_t>(st));
+    return last();
+}
+REF_API int ref_add_fp32(float* a, float* b, float* out, size_t n, void* st) {
+    elementwise_ops_fp32<kElementwiseAdd>(a, b, out, n, 1.f, nullptr, 0.f, 1.f, static_cast<cudaStream_t>(st));
+    return last();
+}
+REF_API int ref_relu2_fp32(float* u, float* out, size_t n, void* st) {
+    elementwise_ops_fp32<kElementwiseRelu2>(u, u, out, n, 1.f, nullptr, 0.f, 1.f, static_cast<cudaStream_t>(st));
+    return last();
+}
+
+// Hidden is a template parameter in the reference (binding.cu uses 3136; its tests also use 128).
+REF_API int ref_embedding_i64(const void* table, const int64_t* ids, void* out, size_t num_tokens, int hidden, void* stv) {
+    cudaStream_t st = static_cast<cudaStream_t>(stv);
+    auto T = static_cast<const bf16*>(table);
+    auto O = static_cast<bf16*>(out);
+    switch (hidden) {
+        case 128: embedding_lookup<128>(T, ids, O, num_tokens, st); break;
+        case 3136: embedding_lookup<3136>(T, ids, O, num_tokens, st); break;
+        default: return -1;
+    }
+    return last();
+}
+
+REF_API int ref_set_device(int d) { return static_cast<int>(cudaSetDevice(d)); }

@@ -1,0 +1,162 @@
+"""TEST INFRASTRUCTURE — the CPU oracle.  Never imported by the product package.
+
+Restates, in torch on the CPU, the formulation of each hot-path op that the
+reference's golden emitters use (paths relative to the reference root):
+
+  plain_rmsnorm   tools/dump_mlp_block.py:28-31 (same text at tools/dump_mamba_block.py:89-92,
+                  tools/dump_attention_block.py:38-41, tools/ref_full_model.py:73-75)
+  gated_rmsnorm   tools/dump_mamba_block.py:81-86 (tools/ref_full_model.py:76-80)
+  relu2           tools/dump_mlp_block.py:49      (tools/ref_full_model.py:137)
+  residual_add    tools/dump_mlp_block.py:53
+  embedding       tools/ref_full_model.py:140
+
+The bf16 forms evaluate the same formulas in fp32 on the upcast bf16 inputs and
+round the result to bf16 (round to nearest even); the fused add+norm rounds the
+residual sum to bf16 BEFORE the norm, because the reference writes the sum as a
+bf16 tensor (ops/elementwise.cuh:241-245) that the next block's RMSNorm reads
+back (ops/reduce.cuh:154-171).
+
+Pinned: tests/test_oracle.py checks every function here against fixtures in
+tests/golden/ that were produced by the reference's own functions and by its
+unmodified dump scripts (tests/golden/make_golden.py).
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+EPS = 1e-5
+
+
+# --- the five formulas, fp32 ---------------------------------------------------
+
+def plain_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = EPS) -> torch.Tensor:
+    x = x.float()
+    var = x.pow(2).mean(-1, keepdim=True)
+    return (x * torch.rsqrt(var + eps)) * weight
+
+
+def gated_rmsnorm(x: torch.Tensor, weight: torch.Tensor, z: torch.Tensor, group_size: int,
+                  eps: float = EPS) -> torch.Tensor:
+    x = x.float() * F.silu(z.float())
+    xg = x.reshape(*x.shape[:-1], x.shape[-1] // group_size, group_size)
+    rstd = torch.rsqrt(xg.pow(2).mean(-1, keepdim=True) + eps)
+    return (xg * rstd).reshape(x.shape) * weight
+
+
+def relu2(u: torch.Tensor) -> torch.Tensor:
+    return F.relu(u.float()).pow(2)
+
+
+def residual_add(x: torch.Tensor, r: torch.Tensor) -> torch.Tensor:
+    return x + r
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    return F.embedding(ids.long(), table)
+
+
+# --- bf16 forms (bf16 storage, fp32 math, one rounding per stored tensor) -------
+
+def rmsnorm_bf16(x: torch.Tensor, w: torch.Tensor, eps: float = EPS) -> torch.Tensor:
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.float32
+    return plain_rmsnorm(x, w, eps).to(torch.bfloat16)
+
+
+def add_bf16(x: torch.Tensor, r: torch.Tensor) -> torch.Tensor:
+    assert x.dtype == torch.bfloat16 and r.dtype == torch.bfloat16
+    return (x.float() + r.float()).to(torch.bfloat16)
+
+
+def add_rmsnorm_bf16(x: torch.Tensor, r: torch.Tensor, w: torch.Tensor, eps: float = EPS):
+    out_res = add_bf16(x, r)
+    return out_res, rmsnorm_bf16(out_res, w, eps)
+
+
+def gated_rmsnorm_bf16(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, group_size: int,
+                       eps: float = EPS) -> torch.Tensor:
+    assert y.dtype == torch.bfloat16 and z.dtype == torch.bfloat16 and w.dtype == torch.float32
+    return gated_rmsnorm(y, w, z, group_size, eps).to(torch.bfloat16)
+
+
+def relu2_bf16(u: torch.Tensor) -> torch.Tensor:
+    assert u.dtype == torch.bfloat16
+    return relu2(u).to(torch.bfloat16)
+
+
+# --- comparison helpers ----------------------------------------------------------
+
+def bf16_ordered(t: torch.Tensor) -> torch.Tensor:
+    """Maps bf16 values to integers that are monotone in the value (+0 and -0 both map to 0)."""
+    bits = t.contiguous().view(torch.int16).to(torch.int32) & 0xFFFF
+    mag = bits & 0x7FFF
+    return torch.where((bits & 0x8000) != 0, -mag, mag)
+
+
+def bf16_ulp_distance(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Element-wise distance in bf16 units in the last place; NaN vs NaN counts as 0, NaN vs number as 2^16."""
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.shape == b.shape
+    d = (bf16_ordered(a) - bf16_ordered(b)).abs()
+    na, nb = torch.isnan(a), torch.isnan(b)
+    d = torch.where(na & nb, torch.zeros_like(d), d)
+    d = torch.where(na ^ nb, torch.full_like(d, 1 << 16), d)
+    return d
+
+
+def ulp_report(got: torch.Tensor, want: torch.Tensor) -> dict:
+    d = bf16_ulp_distance(got.cpu(), want.cpu())
+    n = d.numel()
+    return {"max_ulp": int(d.max()) if n else 0,
+            "mismatch": int((d != 0).sum()),
+            "mismatch_frac": float((d != 0).sum()) / max(n, 1),
+            "n": n}
+
+
+# --- seeded inputs of the benchmark configurations --------------------------------
+# Every tensor is drawn in fp32 from torch.Generator().manual_seed(seed) and then cast.
+
+def _gen(seed: int) -> torch.Generator:
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    return g
+
+
+def norm_weight(cols: int, g: torch.Generator) -> torch.Tensor:
+    return 1.0 + 0.1 * torch.randn(cols, generator=g, dtype=torch.float32)
+
+
+def cfg0_inputs(rows: int = 512, cols: int = 3136, seed: int = 0):
+    """fp32 RMSNorm: x ~ N(0,1), w = 1 + 0.1 N(0,1)."""
+    g = _gen(seed)
+    x = torch.randn(rows, cols, generator=g, dtype=torch.float32)
+    return x, norm_weight(cols, g)
+
+
+def cfg1_inputs(T: int, cols: int = 3136, seed: int = 0):
+    """bf16 residual add + RMSNorm: x, r ~ N(0,1) -> bf16, w fp32."""
+    g = _gen(seed)
+    x = torch.randn(T, cols, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    r = torch.randn(T, cols, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    return x, r, norm_weight(cols, g)
+
+
+def cfg2_inputs(T: int, cols: int = 6144, seed: int = 0):
+    """bf16 gated RMSNorm: y, z ~ N(0,1) -> bf16, w fp32."""
+    g = _gen(seed)
+    y = torch.randn(T, cols, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    z = torch.randn(T, cols, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    return y, z, norm_weight(cols, g)
+
+
+def cfg3_inputs(T: int, cols: int = 12544, seed: int = 0):
+    """bf16 relu^2: u ~ N(0, 2^2) -> bf16."""
+    g = _gen(seed)
+    return (2.0 * torch.randn(T, cols, generator=g, dtype=torch.float32)).to(torch.bfloat16)
+
+
+def cfg4_inputs(T: int, vocab: int = 131072, hidden: int = 3136, seed: int = 0, ids_dtype=torch.int32):
+    """Embedding: table ~ N(0, 0.02^2) -> bf16, ids uniform in [0, vocab)."""
+    g = _gen(seed)
+    table = (0.02 * torch.randn(vocab, hidden, generator=g, dtype=torch.float32)).to(torch.bfloat16)
+    ids = torch.randint(0, vocab, (T,), generator=g, dtype=torch.int64).to(ids_dtype)
+    return table, ids

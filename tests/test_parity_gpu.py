@@ -1,0 +1,367 @@
+"""GPU parity tests: every entry point of libnemotron_b200.so (called through the C ABI) against the CPU
+oracle on identical seeded inputs.  Bars: embedding / add / relu^2 bit-exact; norms within 1 bf16 ulp of the
+torch golden formulation (fp32 accumulation, eps = 1e-5); fp32 twins within the reference tests' 1e-5."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import bf16_from_bits, fptr, golden
+from oracle import torch_golden as og
+
+pytestmark = pytest.mark.gpu
+
+BF = torch.bfloat16
+MAX_ULP = 1                 # tolerance for bf16 norm outputs, in bf16 units in the last place
+MAX_MISMATCH_FRAC = 0.02    # share of elements allowed to sit 1 ulp away (accumulation-order effects)
+
+
+@pytest.fixture(scope="module")
+def ops(built_lib):
+    from nemotron_infer_b200 import ops as _ops
+    assert torch.cuda.is_available()
+    built_lib.nmt_set_device(torch.cuda.current_device())
+    return _ops
+
+
+def dev(t):
+    return t.cuda()
+
+
+def assert_ulp(got, want, what, max_ulp=MAX_ULP, max_frac=MAX_MISMATCH_FRAC):
+    rep = og.ulp_report(got, want)
+    assert rep["max_ulp"] <= max_ulp and rep["mismatch_frac"] <= max_frac, f"{what}: {rep}"
+    return rep
+
+
+# ---------------------------------------------------------------------------------------------
+# residual add + RMSNorm / RMSNorm (bf16)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("T", [1, 64, 8192])
+def test_add_rmsnorm_benchmark_config(ops, T):
+    x, r, w = og.cfg1_inputs(T)
+    want_res, want = og.add_rmsnorm_bf16(x, r, w)
+    got_res, got = ops.add_rmsnorm(dev(x), dev(r), dev(w))
+    assert torch.equal(got_res.cpu(), want_res), "out_res must be bit-exact"
+    assert_ulp(got, want, f"add_rmsnorm T={T}")
+
+
+@pytest.mark.parametrize("T", [1, 64, 8192])
+def test_rmsnorm_benchmark_width(ops, T):
+    x, _, w = og.cfg1_inputs(T)
+    assert_ulp(ops.rmsnorm(dev(x), dev(w)), og.rmsnorm_bf16(x, w), f"rmsnorm T={T}")
+
+
+def test_norm_golden_fixture(ops):
+    d = golden("cfg_bf16.npz")
+    x, r, w = bf16_from_bits(d["cfg1_x"]), bf16_from_bits(d["cfg1_r"]), torch.from_numpy(d["cfg1_w"])
+    res, out = ops.add_rmsnorm(dev(x), dev(r), dev(w))
+    assert torch.equal(res.cpu(), bf16_from_bits(d["cfg1_out_res"]))
+    assert_ulp(out, bf16_from_bits(d["cfg1_out"]), "fixture add_rmsnorm")
+    assert_ulp(ops.rmsnorm(dev(x), dev(w)), bf16_from_bits(d["cfg1_plain_out"]), "fixture rmsnorm")
+
+
+@pytest.mark.parametrize("cols", [8, 64, 256, 520, 1024, 2048, 3136, 4096, 4104, 12544, 40000])
+@pytest.mark.parametrize("rows", [1, 3, 37])
+def test_norm_shapes(ops, rows, cols):
+    g = torch.Generator().manual_seed(rows * 100003 + cols)
+    x = (3 * torch.randn(rows, cols, generator=g)).to(BF)
+    r = torch.randn(rows, cols, generator=g).to(BF)
+    w = og.norm_weight(cols, g)
+    want_res, want = og.add_rmsnorm_bf16(x, r, w)
+    got_res, got = ops.add_rmsnorm(dev(x), dev(r), dev(w))
+    assert torch.equal(got_res.cpu(), want_res)
+    assert_ulp(got, want, f"add_rmsnorm {rows}x{cols}", max_frac=0.05)
+    assert_ulp(ops.rmsnorm(dev(x), dev(w)), og.rmsnorm_bf16(x, w), f"rmsnorm {rows}x{cols}", max_frac=0.05)
+
+
+def test_norm_in_place_and_ragged_grid(ops):
+    x, r, w = og.cfg1_inputs(1000)            # 1000 rows: not a multiple of the warps per CTA
+    want_res, want = og.add_rmsnorm_bf16(x, r, w)
+    xd, rd, wd = dev(x), dev(r), dev(w)
+    out = torch.empty_like(xd)
+    ops.add_rmsnorm(xd, rd, wd, out_res=xd, out=out)       # residual stream updated in place
+    assert torch.equal(xd.cpu(), want_res)
+    assert_ulp(out, want, "in-place add_rmsnorm")
+    y = dev(x)
+    ops.rmsnorm(y, wd, out=y)                               # y aliases x
+    assert_ulp(y, og.rmsnorm_bf16(x, w), "in-place rmsnorm")
+
+
+def test_norm_zero_rows_and_extreme_values(ops):
+    w = torch.ones(3136)
+    ops.rmsnorm(torch.empty(0, 3136, dtype=BF, device="cuda"), dev(w))
+    ops.add_rmsnorm(torch.empty(0, 3136, dtype=BF, device="cuda"), torch.empty(0, 3136, dtype=BF, device="cuda"), dev(w))
+    # an all-zero row normalises to zero (eps keeps rsqrt finite); huge values do not overflow the fp32 sum
+    x = torch.zeros(3, 3136, dtype=BF)
+    x[1] = 1e18
+    x[2, ::2] = -3e-20
+    assert_ulp(ops.rmsnorm(dev(x), dev(w)), og.rmsnorm_bf16(x, w), "extreme rows")
+
+
+def test_tuned_launch_shapes_give_the_same_answer(ops):
+    x, r, w = og.cfg1_inputs(777)
+    want_res, want = og.add_rmsnorm_bf16(x, r, w)
+    try:
+        for block, per_sm in ((128, 0), (64, 2), (256, 1), (96, 4)):
+            ops.tune("norm.block", block)
+            ops.tune("norm.ctas_per_sm", per_sm)
+            res, out = ops.add_rmsnorm(dev(x), dev(r), dev(w))
+            assert torch.equal(res.cpu(), want_res)
+            assert_ulp(out, want, f"block={block} per_sm={per_sm}")
+    finally:
+        ops.tune("norm.block", 0)
+        ops.tune("norm.ctas_per_sm", 0)
+
+
+def test_rmsnorm_fp32_cpu_golden_config(ops):
+    x, w = og.cfg0_inputs()                                 # x[512, 3136] fp32, the CPU-golden configuration
+    got = ops.rmsnorm(dev(x), dev(w)).cpu()
+    torch.testing.assert_close(got, og.plain_rmsnorm(x, w), rtol=1e-5, atol=1e-5)
+    d = golden("cfg0_fp32.npz")
+    torch.testing.assert_close(got[:8], torch.from_numpy(d["out"]), rtol=1e-5, atol=1e-5)
+
+
+def test_fp32_twins_match_the_dump_script_stages(ops):
+    d = golden("dump_mlp_block.npz")
+    x = torch.from_numpy(d["input"]).reshape(8, 64)
+    got = ops.rmsnorm(dev(x), dev(torch.from_numpy(d["block_norm_w"]))).cpu()
+    torch.testing.assert_close(got.reshape(-1), torch.from_numpy(d["normed"]), rtol=1e-5, atol=1e-5)
+    up = torch.from_numpy(d["up"])
+    assert torch.equal(ops.relu2(dev(up)).cpu(), torch.from_numpy(d["act"]))
+    res = ops.add(dev(torch.from_numpy(d["input"])), dev(torch.from_numpy(d["down"]))).cpu()
+    assert torch.equal(res, torch.from_numpy(d["expected"]))
+    m = golden("dump_mamba_block.npz")
+    y = torch.from_numpy(m["scan_y"]).reshape(24, 64)
+    z = torch.from_numpy(m["gate"]).reshape(24, 64)
+    got = ops.rmsnorm_gated(dev(y), dev(z), dev(torch.from_numpy(m["gnorm_w"])), 32).cpu()
+    torch.testing.assert_close(got.reshape(-1), torch.from_numpy(m["gnormed"]), rtol=1e-5, atol=1e-5)
+
+
+# ---------------------------------------------------------------------------------------------
+# gated RMSNorm
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("cols,gs,T", [(6144, 768, 16384), (7680, 960, 4096), (6144, 768, 1), (7680, 960, 3)])
+def test_gated_benchmark_and_model_shapes(ops, cols, gs, T):
+    y, z, w = og.cfg2_inputs(T, cols)
+    want = og.gated_rmsnorm_bf16(y, z, w, gs)
+    assert_ulp(ops.rmsnorm_gated(dev(y), dev(z), dev(w), gs), want, f"gated {T}x{cols}/{gs}")
+
+
+def test_gated_golden_fixture(ops):
+    d = golden("cfg_bf16.npz")
+    for tag, gs in (("cfg2", 768), ("cfg2m", 960)):
+        y, z, w = bf16_from_bits(d[f"{tag}_y"]), bf16_from_bits(d[f"{tag}_z"]), torch.from_numpy(d[f"{tag}_w"])
+        assert_ulp(ops.rmsnorm_gated(dev(y), dev(z), dev(w), gs), bf16_from_bits(d[f"{tag}_out"]), tag)
+
+
+@pytest.mark.parametrize("cols,gs", [(192, 64), (64, 32), (64, 64), (512, 8), (2048, 256), (4096, 2048),
+                                     (8192, 4096), (120, 12), (96, 24), (6144, 6144)])
+@pytest.mark.parametrize("rows", [1, 4, 19])
+def test_gated_shapes(ops, rows, cols, gs):
+    g = torch.Generator().manual_seed(rows * 7919 + cols + gs)
+    y = (3 * torch.randn(rows, cols, generator=g)).to(BF)
+    z = (2 * torch.randn(rows, cols, generator=g)).to(BF)
+    w = 1.5 * torch.randn(cols, generator=g)
+    want = og.gated_rmsnorm_bf16(y, z, w, gs)
+    assert_ulp(ops.rmsnorm_gated(dev(y), dev(z), dev(w), gs), want, f"gated {rows}x{cols}/{gs}", max_frac=0.05)
+
+
+def test_gated_rows_per_iter_variant_and_in_place(ops):
+    y, z, w = og.cfg2_inputs(1001)
+    want = og.gated_rmsnorm_bf16(y, z, w, 768)
+    try:
+        for rpi, block, per_sm in ((2, 256, 0), (1, 128, 3), (2, 64, 5)):
+            ops.tune("gated.rows_per_iter", rpi)
+            ops.tune("gated.block", block)
+            ops.tune("gated.ctas_per_sm", per_sm)
+            yd = dev(y)
+            ops.rmsnorm_gated(yd, dev(z), dev(w), 768, out=yd)      # out aliases y
+            assert_ulp(yd, want, f"gated rpi={rpi} block={block}")
+    finally:
+        for k in ("gated.rows_per_iter", "gated.block", "gated.ctas_per_sm"):
+            ops.tune(k, 0)
+
+
+def test_gated_saturated_gates(ops):
+    # very negative gates drive silu to 0, very positive ones to z: neither may produce NaN/Inf
+    y, z, w = og.cfg2_inputs(4)
+    z[0] = -60.0
+    z[1] = 60.0
+    z[2, ::3] = -20.0
+    want = og.gated_rmsnorm_bf16(y, z, w, 768)
+    got = ops.rmsnorm_gated(dev(y), dev(z), dev(w), 768)
+    assert torch.isfinite(got.float()).all()
+    assert_ulp(got, want, "saturated gates", max_frac=0.05)
+
+
+def test_gated_fp32_twin(ops, oracle_c):
+    rng = np.random.default_rng(1)
+    rows, cols, gs = 4, 192, 64                              # the reference's fp32 test shape (test_reduce.cu:480)
+    x = rng.uniform(-3, 3, (rows, cols)).astype(np.float32)
+    z = rng.uniform(-2, 2, (rows, cols)).astype(np.float32)
+    w = rng.uniform(-1.5, 1.5, cols).astype(np.float32)
+    want = np.empty_like(x)
+    oracle_c.orc_gated_f32(fptr(x), fptr(want), fptr(w), fptr(z), rows, cols, gs, 1e-5)
+    got = ops.rmsnorm_gated(dev(torch.from_numpy(x)), dev(torch.from_numpy(z)), dev(torch.from_numpy(w)), gs).cpu()
+    np.testing.assert_allclose(got.numpy(), want, atol=1e-5, rtol=0)
+    torch.testing.assert_close(got, og.gated_rmsnorm(torch.from_numpy(x), torch.from_numpy(w), torch.from_numpy(z), gs),
+                               rtol=1e-5, atol=1e-5)
+
+
+# ---------------------------------------------------------------------------------------------
+# relu^2 and add
+# ---------------------------------------------------------------------------------------------
+def test_relu2_benchmark_config_is_bit_exact(ops):
+    u = og.cfg3_inputs(8192)
+    assert torch.equal(ops.relu2(dev(u)).cpu(), og.relu2_bf16(u))
+
+
+def test_relu2_fixture_specials_and_sizes(ops):
+    d = golden("cfg_bf16.npz")
+    u = bf16_from_bits(d["cfg3_u"])
+    assert torch.equal(ops.relu2(dev(u)).cpu(), bf16_from_bits(d["cfg3_out"]))
+    s = torch.tensor([0.0, -0.0, 1.0, -1.0, float("inf"), -float("inf"), float("nan"), 3.0e19, 1e-30, -1e-30,
+                      2.0 ** -70, 255.0, 1.0078125, -3.5, 65280.0, 1.8e19], dtype=BF)
+    got, want = ops.relu2(dev(s)).cpu(), og.relu2_bf16(s)
+    assert torch.equal(torch.isnan(got), torch.isnan(want))
+    assert torch.equal(got[~torch.isnan(got)].view(torch.int16), want[~torch.isnan(want)].view(torch.int16))
+    for n in (8, 16, 1024, 8 * 2047, 8 * 2048 + 8, 8 * 100003):
+        u = (2 * torch.randn(n, generator=torch.Generator().manual_seed(n))).to(BF)
+        ud = dev(u)
+        ops.relu2(ud, out=ud)                                   # in place
+        assert torch.equal(ud.cpu(), og.relu2_bf16(u)), n
+    ops.relu2(torch.empty(0, dtype=BF, device="cuda"))
+
+
+def test_every_bf16_value_through_relu2_and_add(ops):
+    allbits = torch.arange(0, 1 << 16, dtype=torch.int32).to(torch.int16).view(BF)
+    got, want = ops.relu2(dev(allbits)).cpu(), og.relu2_bf16(allbits)
+    nan = torch.isnan(want)
+    assert torch.equal(torch.isnan(got), nan)
+    assert torch.equal(got[~nan].view(torch.int16), want[~nan].view(torch.int16))
+    # add: every value against a few partners (finite only: Inf-Inf NaN payloads are not part of the contract)
+    fin = allbits[torch.isfinite(allbits.float())]
+    fin = fin[: fin.numel() // 8 * 8]
+    for partner in (1.0, -1.0078125, 3.0e-5, 0.0):
+        b = torch.full_like(fin, partner)
+        got, want = ops.add(dev(fin), dev(b)).cpu(), og.add_bf16(fin, b)
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), partner
+
+
+def test_add_bf16_bit_exact_and_unroll_variants(ops):
+    x, r, _ = og.cfg1_inputs(2050)
+    want = og.add_bf16(x, r)
+    try:
+        for unroll, block, per_sm in ((8, 256, 0), (1, 128, 0), (2, 512, 0), (4, 1024, 1), (16, 64, 3)):
+            ops.tune("ew.unroll", unroll)
+            ops.tune("ew.block", block)
+            ops.tune("ew.ctas_per_sm", per_sm)
+            assert torch.equal(ops.add(dev(x), dev(r)).cpu(), want), (unroll, block)
+            u = og.cfg3_inputs(3)
+            assert torch.equal(ops.relu2(dev(u)).cpu(), og.relu2_bf16(u)), (unroll, block)
+    finally:
+        for k in ("ew.unroll", "ew.block", "ew.ctas_per_sm"):
+            ops.tune(k, 0)
+
+
+def test_elementwise_fp32_twins(ops):
+    g = torch.Generator().manual_seed(5)
+    for n in (1, 7, 1024, 100003):
+        a, b = torch.randn(n, generator=g), torch.randn(n, generator=g)
+        assert torch.equal(ops.add(dev(a), dev(b)).cpu(), a + b)
+        assert torch.equal(ops.relu2(dev(a)).cpu(), og.relu2(a))
+
+
+# ---------------------------------------------------------------------------------------------
+# embedding gather
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("ids_dtype", [torch.int32, torch.int64])
+def test_embedding_benchmark_config_is_bit_exact(ops, ids_dtype):
+    table, ids = og.cfg4_inputs(65536, ids_dtype=ids_dtype)
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ops.embedding(dev(table), dev(ids), err_flag=flag).cpu()
+    assert torch.equal(got.view(torch.int16), og.embedding(ids, table).view(torch.int16))
+    assert int(flag.item()) == 0
+
+
+def test_embedding_reference_test_patterns(ops):
+    # tests/ops/test_embedding.cu:57-167: ramp tables, sequential / strided / first-middle-last ids
+    def ramp(n, mod, scale, off):
+        i = torch.arange(n, dtype=torch.int64)
+        v = (i % mod).float() if mod else i.float()
+        return (v * scale - off).to(BF)
+    table = ramp(100 * 128, 97, 0.1, 5.0).reshape(100, 128)
+    ids = torch.arange(16, dtype=torch.int64)
+    assert torch.equal(ops.embedding(dev(table), dev(ids)).cpu().view(torch.int16), table[ids].view(torch.int16))
+    vocab, hidden = 131072, 3136
+    table = ramp(vocab * hidden, 97, 0.1, 5.0).reshape(vocab, hidden)
+    td = dev(table)
+    ids = (torch.arange(64, dtype=torch.int64) * 2047) % vocab
+    assert torch.equal(ops.embedding(td, dev(ids)).cpu().view(torch.int16), table[ids].view(torch.int16))
+    h = vocab // 2
+    ids = torch.tensor(list(range(8)) + list(range(h - 4, h + 4)) + list(range(vocab - 8, vocab)) +
+                       [100, 200, 300, 400, 500, 600, 700, 800], dtype=torch.int64)
+    assert torch.equal(ops.embedding(td, dev(ids)).cpu().view(torch.int16), table[ids].view(torch.int16))
+
+
+def test_embedding_fixture_widths_and_bad_ids(ops):
+    d = golden("cfg_bf16.npz")
+    table, ids = bf16_from_bits(d["cfg4_table"]), torch.from_numpy(d["cfg4_ids"])
+    want = bf16_from_bits(d["cfg4_out"])
+    for dt in (torch.int64, torch.int32):
+        assert torch.equal(ops.embedding(dev(table), dev(ids.to(dt))).cpu().view(torch.int16), want.view(torch.int16))
+    for hidden in (8, 128, 1000, 3136, 4096, 8192, 12544):
+        g = torch.Generator().manual_seed(hidden)
+        t = torch.randn(33, hidden, generator=g).to(BF)
+        i = torch.randint(0, 33, (50,), generator=g)
+        assert torch.equal(ops.embedding(dev(t), dev(i)).cpu().view(torch.int16), t[i].view(torch.int16)), hidden
+    # out-of-range ids: never dereferenced, row zero-filled, flag raised
+    bad = ids.clone()
+    bad[3], bad[7] = 64, -1
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = ops.embedding(dev(table), dev(bad), err_flag=flag).cpu()
+    good = torch.ones(bad.numel(), dtype=torch.bool)
+    good[3] = good[7] = False
+    assert int(flag.item()) == 1
+    assert torch.equal(got[good].view(torch.int16), want[good].view(torch.int16))
+    assert (got[~good].view(torch.int16) == 0).all()
+    assert ops.embedding(dev(table), torch.empty(0, dtype=torch.int64, device="cuda")).shape == (0, 3136)
+
+
+# ---------------------------------------------------------------------------------------------
+# the reference's own kernels, recompiled for sm_100a, as a second checker
+# ---------------------------------------------------------------------------------------------
+def test_against_reference_kernels(ops, ref_kernels):
+    if ref_kernels is None:
+        pytest.skip("oracle/_ref/libnemotron_ref.so not built (needs the reference checkout at build time)")
+    R = ref_kernels
+    R.ref_set_device(torch.cuda.current_device())
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    sz = ctypes.c_size_t
+    # add and relu^2: bit-identical to the reference kernels
+    x, r, w = (dev(t) for t in og.cfg1_inputs(512))
+    ref = torch.empty_like(x)
+    assert R.ref_add_bf16(p(x), p(r), p(ref), sz(x.numel()), None) == 0
+    assert torch.equal(ops.add(x, r).view(torch.int16), ref.view(torch.int16))
+    u = dev(og.cfg3_inputs(64))
+    ref = torch.empty_like(u)
+    assert R.ref_relu2_bf16(p(u), p(ref), sz(u.numel()), None) == 0
+    assert torch.equal(ops.relu2(u).view(torch.int16), ref.view(torch.int16))
+    # embedding: bit-identical
+    table, ids = (dev(t) for t in og.cfg4_inputs(4096, vocab=4096, ids_dtype=torch.int64))
+    ref = torch.empty(4096, 3136, dtype=BF, device="cuda")
+    assert R.ref_embedding_i64(p(table), p(ids), p(ref), sz(4096), 3136, None) == 0
+    assert torch.equal(ops.embedding(table, ids).view(torch.int16), ref.view(torch.int16))
+    # norms: the reference multiplies x * (rstd * w), the golden (x * rstd) * w: up to 1 ulp each way
+    ref = torch.empty_like(x)
+    res = ops.add(x, r)
+    assert R.ref_rmsnorm_bf16(p(res), p(ref), p(w), sz(512), sz(3136), ctypes.c_float(1e-5), None) == 0
+    _, got = ops.add_rmsnorm(x, r, w)
+    assert_ulp(got, ref, "vs reference rmsnorm kernel", max_ulp=2, max_frac=0.2)
+    y, z, gw = (dev(t) for t in og.cfg2_inputs(256, 7680))
+    ref = torch.empty_like(y)
+    assert R.ref_rmsnorm_gated_bf16(p(y), p(z), p(gw), p(ref), sz(256), sz(7680), sz(960), ctypes.c_float(1e-5), None) == 0
+    assert_ulp(ops.rmsnorm_gated(y, z, gw, 960), ref, "vs reference gated kernel", max_ulp=2, max_frac=0.2)
+    torch.cuda.synchronize()
