@@ -145,6 +145,10 @@ int nmt_embedding_bf16_i32(const void* table, const int32_t* ids, void* out,
  * defaults are the measured-best settings. */
 int nmt_tune_set(const char* key, int value);
 int nmt_tune_get(const char* key, int* value);
+/* The staged (TMA) kernels bound every mbarrier wait; a wait that runs out is counted on the device and the
+ * kernel winds down instead of spinning.  Returns the number of such timeouts on the current device since
+ * load (synchronises the device; 0 in a healthy run, -1 if the counter cannot be read). */
+int64_t nmt_device_wait_timeouts(void);
 /* Number of kernel launches this library has enqueued since load (all threads). */
 int64_t nmt_launch_count(void);
 

@@ -38,6 +38,7 @@ PROTOTYPES = {
     "nmt_tune_set": (_int, [C.c_char_p, _int]),
     "nmt_tune_get": (_int, [C.c_char_p, C.POINTER(_int)]),
     "nmt_launch_count": (_i64, []),
+    "nmt_device_wait_timeouts": (_i64, []),
 }
 
 _lock = threading.Lock()

@@ -71,8 +71,8 @@ ew_f32_kernel(const float* a, const float* b, float* out, int64_t n) {
 template <int OP>
 static int launch_ew_bf16(const void* a, const void* b, void* out, int64_t n, cudaStream_t st) {
     const int64_t nv = n / 8;
-    int block = tune("ew.block", 256);
-    const int unroll = tune("ew.unroll", 8);
+    int block = tune("ew.block", 512);
+    const int unroll = tune("ew.unroll", 2);
     if (block > 1024) block = 1024;
     block = (block + 31) / 32 * 32;
     const int per_sm = tune("ew.ctas_per_sm", 0);

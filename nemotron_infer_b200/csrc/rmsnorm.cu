@@ -10,6 +10,8 @@
 
 namespace nmt {
 
+constexpr int kDefaultNormVariant = 1;   // 1 = warp-per-row registers, 2 = TMA-staged tiles
+
 template <int SLOTS, bool FUSE_ADD>
 __global__ void __launch_bounds__(256)
 rmsnorm_rowwarp_kernel(const uint4* x, const uint4* r,
@@ -157,6 +159,9 @@ rmsnorm_f32_kernel(const float* __restrict__ x, float* y, const float* __restric
     }
 }
 
+int launch_norm_tma(bool fuse, const void* x, const void* r, const float* w, void* out_res, void* out,
+                    int64_t rows, int64_t cols, float eps, cudaStream_t st);   // rmsnorm_tma.cu
+
 template <bool FUSE_ADD>
 static int launch_norm_bf16(const void* x, const void* r, const float* w, void* out_res, void* out,
                             int64_t rows, int64_t cols, float eps, cudaStream_t st) {
@@ -167,12 +172,16 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
     auto OR = static_cast<uint4*>(out_res);
     auto O = static_cast<uint4*>(out);
 
+    if (tune("norm.variant", kDefaultNormVariant) == 2) {
+        const int s = launch_norm_tma(FUSE_ADD, x, r, w, out_res, out, rows, cols, eps, st);
+        if (s != NMT_ERR_UNSUPPORTED) return s;
+    }
     if (nv > 16 * 32) {
         const int grid = grid_for(rows, 1, kSmCount * 16);
         rmsnorm_rowcta_kernel<FUSE_ADD><<<grid, 256, 0, st>>>(X, R, w, OR, O, rows, nv, inv_cols, eps);
         return finish_launch(1);
     }
-    int block = tune("norm.block", 256);
+    int block = tune("norm.block", 64);
     block = block > 256 ? 256 : (block + 31) / 32 * 32;
     const int wpc = block / 32;
     const int per_sm = tune("norm.ctas_per_sm", 0);

@@ -155,7 +155,7 @@ int nmt_rmsnorm_gated_bf16(const void* y, const void* z, const float* w, void* o
     }
     const int gv = static_cast<int>(group_size / 8);
     const int slots = (gv + 31) / 32;
-    int block = tune("gated.block", 256);
+    int block = tune("gated.block", 128);
     block = block > 256 ? 256 : (block + 31) / 32 * 32;
     const int wpc = block / 32;
     const int rpi = tune("gated.rows_per_iter", 1);

@@ -53,6 +53,22 @@ static Knob* find_knob(const char* key) {
     for (auto& k : g_knobs) if (std::strcmp(k.key, key) == 0) return &k;
     return nullptr;
 }
+// Each TMA translation unit keeps its own device counter of timed-out waits and registers a reader here.
+static cudaError_t (*g_timeout_readers[16])(unsigned int*);
+static int g_n_timeout_readers = 0;
+void register_timeout_reader(cudaError_t (*reader)(unsigned int*)) {
+    if (g_n_timeout_readers < 16) g_timeout_readers[g_n_timeout_readers++] = reader;
+}
+int64_t read_wait_timeouts() {
+    int64_t total = 0;
+    for (int i = 0; i < g_n_timeout_readers; ++i) {
+        unsigned int v = 0;
+        if (g_timeout_readers[i](&v) != cudaSuccess) return -1;
+        total += v;
+    }
+    return total;
+}
+
 int tune(const char* key, int dflt) {
     Knob* k = find_knob(key);
     if (!k) return dflt;
@@ -110,6 +126,7 @@ int nmt_tune_get(const char* key, int* value) {
     *value = k->value.load(std::memory_order_relaxed);
     return NMT_OK;
 }
+int64_t nmt_device_wait_timeouts(void) { return nmt::read_wait_timeouts(); }
 int64_t nmt_launch_count(void) { return nmt::g_launches.load(std::memory_order_relaxed); }
 
 }  // extern "C"

@@ -115,6 +115,31 @@ def test_tuned_launch_shapes_give_the_same_answer(ops):
         ops.tune("norm.ctas_per_sm", 0)
 
 
+@pytest.mark.parametrize("rows_per_tile,stages,per_sm", [(4, 4, 1), (8, 2, 1), (2, 3, 2), (1, 8, 3), (3, 2, 1)])
+def test_tma_staged_norm_variant(ops, built_lib, rows_per_tile, stages, per_sm):
+    try:
+        ops.tune("norm.variant", 2)
+        ops.tune("norm.tma_rows", rows_per_tile)
+        ops.tune("norm.tma_stages", stages)
+        ops.tune("norm.ctas_per_sm", per_sm)
+        for T, cols in ((1, 3136), (5, 3136), (2051, 3136), (8192, 3136), (33, 1024), (70, 4096), (9, 64)):
+            g = torch.Generator().manual_seed(T * 31 + cols)
+            x = torch.randn(T, cols, generator=g).to(BF)
+            r = torch.randn(T, cols, generator=g).to(BF)
+            w = og.norm_weight(cols, g)
+            want_res, want = og.add_rmsnorm_bf16(x, r, w)
+            xd = dev(x)
+            out = torch.empty_like(xd)
+            ops.add_rmsnorm(xd, dev(r), dev(w), out_res=xd, out=out)       # in place on the residual stream
+            assert torch.equal(xd.cpu(), want_res), (T, cols)
+            assert_ulp(out, want, f"tma add_rmsnorm {T}x{cols}", max_frac=0.05)
+            assert_ulp(ops.rmsnorm(dev(x), dev(w)), og.rmsnorm_bf16(x, w), f"tma rmsnorm {T}x{cols}", max_frac=0.05)
+        assert built_lib.nmt_device_wait_timeouts() == 0
+    finally:
+        for k in ("norm.variant", "norm.tma_rows", "norm.tma_stages", "norm.ctas_per_sm"):
+            ops.tune(k, 0)
+
+
 def test_rmsnorm_fp32_cpu_golden_config(ops):
     x, w = og.cfg0_inputs()                                 # x[512, 3136] fp32, the CPU-golden configuration
     got = ops.rmsnorm(dev(x), dev(w)).cpu()
@@ -363,5 +388,14 @@ def test_against_reference_kernels(ops, ref_kernels):
     y, z, gw = (dev(t) for t in og.cfg2_inputs(256, 7680))
     ref = torch.empty_like(y)
     assert R.ref_rmsnorm_gated_bf16(p(y), p(z), p(gw), p(ref), sz(256), sz(7680), sz(960), ctypes.c_float(1e-5), None) == 0
-    assert_ulp(ops.rmsnorm_gated(y, z, gw, 960), ref, "vs reference gated kernel", max_ulp=2, max_frac=0.2)
     torch.cuda.synchronize()
+    # The reference's block_group_reduce_sum lets all 32 lanes of warp 0 store different partial sums to the
+    # same shared-memory word (ops/reduce.cuh:280-287); which lane wins is undefined, and on sm_100a the
+    # winner is not lane 0, so its gated output is wrong there.  Ours is checked against the golden
+    # formulation; the reference kernel is only required to agree when its race happens to resolve correctly.
+    want = og.gated_rmsnorm_bf16(y.cpu(), z.cpu(), gw.cpu(), 960)
+    assert_ulp(ops.rmsnorm_gated(y, z, gw, 960), want, "gated vs golden")
+    ref_rep = og.ulp_report(ref, want)
+    print("reference gated kernel vs golden on this GPU:", ref_rep)
+    if ref_rep["max_ulp"] <= 2:
+        assert_ulp(ops.rmsnorm_gated(y, z, gw, 960), ref, "vs reference gated kernel", max_ulp=2, max_frac=0.2)
