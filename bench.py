@@ -306,7 +306,7 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> dict | None:
         "hbm_gbs": round(gbs, 1), "hbm_gbs_per_gpu": round(gbs / world, 1),
         "hbm_frac_of_measured_peak": round(gbs / world / peak, 4),
         "hbm_frac_of_nominal_8000": round(gbs / world / NOMINAL_HBM_GBS, 4),
-        "roofline": dict(kernels["add_rmsnorm"], kernel="rmsnorm_rowwarp_kernel<13,true> (fused add+RMSNorm)",
+        "roofline": dict(kernels["add_rmsnorm"], kernel="rmsnorm_ctarow_kernel<3,true> (fused residual add + RMSNorm, 3136 wide)",
                          peak_source=peak_src),
         "kernels": kernels,
         "e2e": {"value": round(tokens_total / e2e_s, 1), "unit": "tokens/s",

@@ -3,7 +3,7 @@
 // Register variant: a CTA takes a tile of blockDim * U 16-byte vectors; every
 // thread issues its U loads (stride blockDim, so each warp request is 512
 // contiguous bytes) before the first use, which keeps U * 16 B * threads in
-// flight per CTA.  The arithmetic is packed bf16x2: max.NaN against zero then a
+// flight per CTA.  The arithmetic is packed bf16x2: a relu-clamped FMA then a
 // bf16 multiply (x*x is exact in fp32, so the single bf16 rounding equals
 // "square in fp32, round to nearest even"); add is one bf16x2 add (single
 // rounding of the exact sum).
@@ -14,9 +14,11 @@ namespace nmt {
 enum { kOpRelu2 = 0, kOpAdd = 1 };
 
 __device__ __forceinline__ uint32_t relu2_bf16x2(uint32_t u) {
+    // fma.rn.relu.bf16x2 (x * 1 + 0, clamped at zero): one FMA-pipe instruction per pair; NaN stays NaN
+    // and -0 becomes +0.  The reference uses the same instruction (ops/elementwise.cuh:256-268).
     __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&u);
-    const __nv_bfloat162 zero = __float2bfloat162_rn(0.f);
-    x = __hmax2_nan(x, zero);          // NaN propagates, -0 -> +0
+    const __nv_bfloat162 one = __float2bfloat162_rn(1.f), zero = __float2bfloat162_rn(0.f);
+    x = __hfma2_relu(x, one, zero);
     x = __hmul2(x, x);
     return *reinterpret_cast<uint32_t*>(&x);
 }

@@ -55,6 +55,15 @@ embedding_generic_kernel(const uint4* __restrict__ table, const IdT* __restrict_
 }
 
 template <typename IdT>
+int launch_embedding_tma(const void* table, const IdT* ids, void* out, int64_t num_tokens, int64_t hidden,
+                         int64_t vocab, int32_t* err_flag, cudaStream_t st);   // embedding_tma.cu
+
+// 1 = warp-per-row registers, 2 = TMA relay.  Both reach the same bandwidth on a large batch (the random-row
+// access pattern is the limit); the relay does it with two instructions per row instead of 26 per lane, so it
+// is the default for prefill-sized batches, while short batches keep the single-hop register path.
+constexpr int kRelayMinTokens = 4096;
+
+template <typename IdT>
 static int launch_embedding(const void* table, const IdT* ids, void* out, int64_t num_tokens,
                             int64_t hidden, int64_t vocab, int32_t* err_flag, cudaStream_t st) {
     if (num_tokens < 0 || hidden <= 0 || (hidden % 8) != 0) return NMT_ERR_SHAPE;
@@ -63,6 +72,10 @@ static int launch_embedding(const void* table, const IdT* ids, void* out, int64_
     if (!aligned16(table) || !aligned16(out) || (reinterpret_cast<uintptr_t>(ids) % sizeof(IdT)) != 0 ||
         (err_flag && !aligned4(err_flag)))
         return NMT_ERR_ALIGN;
+    if (tune("emb.variant", num_tokens >= kRelayMinTokens ? 2 : 1) == 2) {
+        const int s = launch_embedding_tma<IdT>(table, ids, out, num_tokens, hidden, vocab, err_flag, st);
+        if (s != NMT_ERR_UNSUPPORTED) return s;
+    }
     const int64_t nv = hidden / 8;
     auto T = static_cast<const uint4*>(table);
     auto O = static_cast<uint4*>(out);

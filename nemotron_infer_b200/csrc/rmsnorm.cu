@@ -10,7 +10,7 @@
 
 namespace nmt {
 
-constexpr int kDefaultNormVariant = 1;   // 1 = warp-per-row registers, 2 = TMA-staged tiles
+constexpr int kDefaultNormVariant = 3;   // 1 = warp-per-row registers, 2 = TMA-staged tiles, 3 = CTA-per-row registers
 
 template <int SLOTS, bool FUSE_ADD>
 __global__ void __launch_bounds__(256)
@@ -62,6 +62,74 @@ rmsnorm_rowwarp_kernel(const uint4* x, const uint4* r,
 #pragma unroll
         for (int s = 0; s < SLOTS; ++s) {
             const int v = s * 32 + lane;
+            if (v < nv) {
+                float f[8];
+                unpack8(a[s], f);
+                const float4 w0 = ld_weight4(w + v * 8);
+                const float4 w1 = ld_weight4(w + v * 8 + 4);
+                f[0] = (f[0] * rstd) * w0.x; f[1] = (f[1] * rstd) * w0.y;
+                f[2] = (f[2] * rstd) * w0.z; f[3] = (f[3] * rstd) * w0.w;
+                f[4] = (f[4] * rstd) * w1.x; f[5] = (f[5] * rstd) * w1.y;
+                f[6] = (f[6] * rstd) * w1.z; f[7] = (f[7] * rstd) * w1.w;
+                st_stream(out + row * nv + v, pack8(f));
+            }
+        }
+    }
+}
+
+// CTA-per-row register variant: blockDim threads share one row (thread t owns vectors t, t + blockDim, ...),
+// so each thread holds only SLOTS = ceil(vectors / blockDim) vectors of x and r.  Few registers per thread
+// means many resident warps (the occupancy the memory system needs), and the price is one block barrier
+// per row for the sum of squares.  Partial sums are added in a fixed order, so results are deterministic.
+template <int SLOTS, bool FUSE_ADD>
+__global__ void __launch_bounds__(512)
+rmsnorm_ctarow_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, uint4* out_res, uint4* out,
+                      int64_t rows, int nv, float inv_cols, float eps) {
+    __shared__ __align__(16) float s_part[2][16];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    int flip = 0;
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, flip ^= 1) {
+        const uint4* xr = x + row * nv;
+        const uint4* rr = FUSE_ADD ? r + row * nv : nullptr;
+        uint4 a[SLOTS], b[SLOTS];
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int v = s * blockDim.x + threadIdx.x;
+            if (v < nv) {
+                a[s] = ld_stream(xr + v);
+                if (FUSE_ADD) b[s] = ld_stream(rr + v);
+            } else {
+                a[s] = make_uint4(0, 0, 0, 0);
+                if (FUSE_ADD) b[s] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            float f[8];
+            unpack8(a[s], f);
+            if (FUSE_ADD) {
+                float g[8];
+                unpack8(b[s], g);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) f[k] += g[k];
+                a[s] = pack8(f);                    // round the residual stream before the norm sees it
+                unpack8(a[s], f);
+                const int v = s * blockDim.x + threadIdx.x;
+                if (v < nv) st_stream(out_res + row * nv + v, a[s]);
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss = fmaf(f[k], f[k], ss);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) s_part[flip][wid] = ss;
+        __syncthreads();
+        float total = 0.f;
+        for (int i = 0; i < nwarps; ++i) total += s_part[flip][i];
+        const float rstd = rsqrtf(total * inv_cols + eps);
+#pragma unroll
+        for (int s = 0; s < SLOTS; ++s) {
+            const int v = s * blockDim.x + threadIdx.x;
             if (v < nv) {
                 float f[8];
                 unpack8(a[s], f);
@@ -176,12 +244,37 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
         const int s = launch_norm_tma(FUSE_ADD, x, r, w, out_res, out, rows, cols, eps, st);
         if (s != NMT_ERR_UNSUPPORTED) return s;
     }
+    if (tune("norm.variant", kDefaultNormVariant) == 3 && nv <= 8 * 512) {
+        // Default shape: about 160 threads per row (392 vectors -> 3 per thread), at most 8 vectors per thread.
+        int block = tune("norm.block", 0);
+        if (block <= 0) {
+            const int want_slots = static_cast<int>((nv + 159) / 160);
+            block = static_cast<int>((nv + want_slots - 1) / want_slots);
+        }
+        block = block > 512 ? 512 : (block + 31) / 32 * 32;
+        const int slots = static_cast<int>((nv + block - 1) / block);
+        const int per_sm = tune("norm.ctas_per_sm", 0);
+        const int grid = grid_for(rows, 1, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);
+#define NMT_CTAROW_CASE(S) \
+    rmsnorm_ctarow_kernel<S, FUSE_ADD><<<grid, block, 0, st>>>(X, R, w, OR, O, rows, (int)nv, inv_cols, eps)
+        if (slots <= 1) NMT_CTAROW_CASE(1);
+        else if (slots <= 2) NMT_CTAROW_CASE(2);
+        else if (slots <= 3) NMT_CTAROW_CASE(3);
+        else if (slots <= 4) NMT_CTAROW_CASE(4);
+        else if (slots <= 5) NMT_CTAROW_CASE(5);
+        else if (slots <= 7) NMT_CTAROW_CASE(7);
+        else if (slots <= 8) NMT_CTAROW_CASE(8);
+        else goto wide;   // more than 8 vectors per thread: fall through to the other variants
+#undef NMT_CTAROW_CASE
+        return finish_launch(1);
+    }
+wide:
     if (nv > 16 * 32) {
         const int grid = grid_for(rows, 1, kSmCount * 16);
         rmsnorm_rowcta_kernel<FUSE_ADD><<<grid, 256, 0, st>>>(X, R, w, OR, O, rows, nv, inv_cols, eps);
         return finish_launch(1);
     }
-    int block = tune("norm.block", 64);
+    int block = tune("norm.block", 64);      // warp-per-row variant
     block = block > 256 ? 256 : (block + 31) / 32 * 32;
     const int wpc = block / 32;
     const int per_sm = tune("norm.ctas_per_sm", 0);

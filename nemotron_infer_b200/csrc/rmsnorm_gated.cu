@@ -11,12 +11,14 @@
 
 namespace nmt {
 
-// z / (1 + exp(-z)) through the SFU: 2^(-z*log2 e) and an approximate reciprocal.
-// Both are good to ~2 ulp of fp32, far below the bf16 rounding of the result.
+// z / (1 + exp(-z)) through the SFU: 2^(-z*log2 e) and an approximate reciprocal, both good to ~2 ulp of
+// fp32, far below the bf16 rounding of the result.  The .ftz forms are single MUFU instructions (the
+// denormal-preserving forms expand into range-scaling sequences that made this kernel issue-bound); the only
+// visible effect is that silu(z) flushes to zero once |silu(z)| < 2^-126 (z below about -87).
 __device__ __forceinline__ float silu_sfu(float z) {
     float e, rcp;
-    asm("ex2.approx.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
-    asm("rcp.approx.f32 %0, %1;" : "=f"(rcp) : "f"(1.0f + e));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(1.0f + e));
     return z * rcp;
 }
 __device__ __forceinline__ float silu_exact(float z) { return z / (1.0f + expf(-z)); }

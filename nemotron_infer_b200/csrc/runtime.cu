@@ -23,7 +23,7 @@ int finish_launch(int n_kernels) {
 struct Knob { const char* key; std::atomic<int> value; };
 static Knob g_knobs[] = {
     // add_rmsnorm / rmsnorm (bf16)
-    {"norm.variant", {0}},        // 0 = auto, 1 = warp-per-row registers, 2 = TMA-staged tiles
+    {"norm.variant", {0}},        // 0 = default (3), 1 = warp-per-row registers, 2 = TMA-staged tiles, 3 = CTA-per-row registers
     {"norm.block", {0}},          // threads per CTA for the warp-per-row kernel
     {"norm.ctas_per_sm", {0}},    // >0: persistent grid of 148*k CTAs; 0: one pass, grid = rows/warps
     {"norm.tma_rows", {0}},       // rows per TMA stage
@@ -42,10 +42,10 @@ static Knob g_knobs[] = {
     {"ew.tma_chunk", {0}},        // bytes per TMA stage
     {"ew.tma_stages", {0}},
     // embedding gather
-    {"emb.variant", {0}},         // 0 = auto, 1 = warp-per-row registers, 2 = TMA row relay
+    {"emb.variant", {0}},         // 0 = by batch size, 1 = warp-per-row registers, 2 = TMA row relay
     {"emb.block", {0}},
     {"emb.ctas_per_sm", {0}},
-    {"emb.tma_rows", {0}},
+    {"emb.relay_warps", {0}},     // relays (warps) per CTA of the TMA variant
     {"emb.tma_stages", {0}},
 };
 static Knob* find_knob(const char* key) {

@@ -104,15 +104,22 @@ def test_tuned_launch_shapes_give_the_same_answer(ops):
     x, r, w = og.cfg1_inputs(777)
     want_res, want = og.add_rmsnorm_bf16(x, r, w)
     try:
-        for block, per_sm in ((128, 0), (64, 2), (256, 1), (96, 4)):
+        for variant, block, per_sm in ((1, 128, 0), (1, 64, 2), (1, 256, 1), (1, 96, 4), (3, 160, 0), (3, 64, 3)):
+            ops.tune("norm.variant", variant)      # 1 = warp per row, 3 = CTA per row
             ops.tune("norm.block", block)
             ops.tune("norm.ctas_per_sm", per_sm)
             res, out = ops.add_rmsnorm(dev(x), dev(r), dev(w))
             assert torch.equal(res.cpu(), want_res)
-            assert_ulp(out, want, f"block={block} per_sm={per_sm}")
+            assert_ulp(out, want, f"variant={variant} block={block} per_sm={per_sm}")
+            for cols in (64, 1024, 4096):
+                xs, rs, ws = og.cfg1_inputs(21, cols)
+                wr, wo = og.add_rmsnorm_bf16(xs, rs, ws)
+                res, out = ops.add_rmsnorm(dev(xs), dev(rs), dev(ws))
+                assert torch.equal(res.cpu(), wr)
+                assert_ulp(out, wo, f"variant={variant} cols={cols}", max_frac=0.05)
     finally:
-        ops.tune("norm.block", 0)
-        ops.tune("norm.ctas_per_sm", 0)
+        for k in ("norm.variant", "norm.block", "norm.ctas_per_sm"):
+            ops.tune(k, 0)
 
 
 @pytest.mark.parametrize("rows_per_tile,stages,per_sm", [(4, 4, 1), (8, 2, 1), (2, 3, 2), (1, 8, 3), (3, 2, 1)])
@@ -353,6 +360,59 @@ def test_embedding_fixture_widths_and_bad_ids(ops):
     assert torch.equal(got[good].view(torch.int16), want[good].view(torch.int16))
     assert (got[~good].view(torch.int16) == 0).all()
     assert ops.embedding(dev(table), torch.empty(0, dtype=torch.int64, device="cuda")).shape == (0, 3136)
+
+
+@pytest.mark.parametrize("stages,warps,per_sm", [(4, 4, 0), (8, 2, 0), (2, 8, 1), (4, 1, 3)])
+def test_embedding_tma_relay_variant(ops, built_lib, stages, warps, per_sm):
+    try:
+        ops.tune("emb.variant", 2)
+        ops.tune("emb.tma_stages", stages)
+        ops.tune("emb.relay_warps", warps)
+        ops.tune("emb.ctas_per_sm", per_sm)
+        for T, vocab, hidden, dt in ((1, 64, 3136, torch.int64), (7, 64, 3136, torch.int32), (8, 50, 128, torch.int64),
+                                    (1000, 4096, 3136, torch.int32), (20001, 8192, 3136, torch.int64), (333, 100, 8, torch.int32),
+                                    (50, 33, 12544, torch.int64)):
+            table, ids = og.cfg4_inputs(T, vocab=vocab, hidden=hidden, seed=T, ids_dtype=dt)
+            flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+            got = ops.embedding(dev(table), dev(ids), err_flag=flag).cpu()
+            assert torch.equal(got.view(torch.int16), og.embedding(ids, table).view(torch.int16)), (T, vocab, hidden)
+            assert int(flag.item()) == 0
+        # bad ids: zero rows + flag, neighbours untouched
+        table, ids = og.cfg4_inputs(100, vocab=64, seed=9, ids_dtype=torch.int64)
+        ids[0], ids[50], ids[99] = 64, -5, 1 << 40
+        flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+        got = ops.embedding(dev(table), dev(ids), err_flag=flag).cpu()
+        bad = torch.zeros(100, dtype=torch.bool)
+        bad[[0, 50, 99]] = True
+        assert int(flag.item()) == 1
+        assert (got[bad].view(torch.int16) == 0).all()
+        assert torch.equal(got[~bad].view(torch.int16), table[ids[~bad]].view(torch.int16))
+        assert built_lib.nmt_device_wait_timeouts() == 0
+    finally:
+        for k in ("emb.variant", "emb.tma_stages", "emb.relay_warps", "emb.ctas_per_sm"):
+            ops.tune(k, 0)
+
+
+@pytest.mark.parametrize("block", [64, 96, 128, 224, 416, 512])
+def test_cta_per_row_norm_variant(ops, block):
+    try:
+        ops.tune("norm.variant", 3)
+        ops.tune("norm.block", block)
+        for T, cols in ((1, 3136), (5, 3136), (2051, 3136), (33, 1024), (70, 4096), (9, 64), (3, 12544)):
+            g = torch.Generator().manual_seed(T * 31 + cols)
+            x = torch.randn(T, cols, generator=g).to(BF)
+            r = torch.randn(T, cols, generator=g).to(BF)
+            w = og.norm_weight(cols, g)
+            want_res, want = og.add_rmsnorm_bf16(x, r, w)
+            xd = dev(x)
+            out = torch.empty_like(xd)
+            ops.add_rmsnorm(xd, dev(r), dev(w), out_res=xd, out=out)
+            assert torch.equal(xd.cpu(), want_res), (T, cols)
+            assert_ulp(out, want, f"cta-row add_rmsnorm {T}x{cols}", max_frac=0.05)
+            assert_ulp(ops.rmsnorm(dev(x), dev(w)), og.rmsnorm_bf16(x, w), f"cta-row rmsnorm {T}x{cols}", max_frac=0.05)
+    finally:
+        ops.tune("norm.variant", 0)
+        ops.tune("norm.block", 0)
 
 
 # ---------------------------------------------------------------------------------------------
