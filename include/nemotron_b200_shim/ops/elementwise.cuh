@@ -1,0 +1,53 @@
+// Source-level drop-in for the reference header ops/elementwise.cuh (see reduce.cuh in this directory for
+// how to use it).  Only the two operators the model's blocks call are provided -- kElementwiseAdd (the
+// residual add, model/mlp_block.cuh:104) and kElementwiseRelu2 (model/mlp_block.cuh:100); instantiating any
+// other operator is a compile-time error rather than a silent fallback.  Signatures follow
+// ops/elementwise.cuh:177-195 and :374-385.
+#ifndef NEMOTRON_B200_SHIM_ELEMENTWISE_CUH
+#define NEMOTRON_B200_SHIM_ELEMENTWISE_CUH
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstddef>
+
+#include "../../nemotron_b200.h"
+
+namespace nemotron::ops {
+
+// Same enumerators and values as the reference (ops/elementwise.cuh:18-27) so call sites compile unchanged.
+enum ElementwiseType {
+    kElementwiseUnknown = -1,
+    kElementwiseAdd = 0,
+    kElementwiseMul,
+    kElementwiseScale,
+    kElementwiseRelu2,
+    kElementwiseSilu,
+    kElementwiseClampSoftplus,
+};
+
+template <ElementwiseType ops_type>
+inline void elementwise_ops_fp32(float* in0, float* in1, float* out0, const size_t size, const float scale = 1.f,
+                                 const float* bias = nullptr, const float clamp_min = 0.f,
+                                 const float clamp_max = 1.f, cudaStream_t stream = nullptr) {
+    static_assert(ops_type == kElementwiseAdd || ops_type == kElementwiseRelu2,
+                  "nemotron_b200 provides only the operators on the model's path: Add and Relu2");
+    (void)scale; (void)bias; (void)clamp_min; (void)clamp_max;
+    if (ops_type == kElementwiseAdd) nmt_add_f32(in0, in1, out0, static_cast<int64_t>(size), stream);
+    else nmt_relu2_f32(in0, out0, static_cast<int64_t>(size), stream);
+}
+
+template <ElementwiseType ops_type>
+inline void elementwise_ops_bf16(const __nv_bfloat16* in0, const __nv_bfloat16* in1, __nv_bfloat16* out0,
+                                 const size_t size, const float scale = 1.f, const __nv_bfloat16* bias = nullptr,
+                                 const float clamp_min = 0.f, const float clamp_max = 1.f,
+                                 cudaStream_t stream = nullptr) {
+    static_assert(ops_type == kElementwiseAdd || ops_type == kElementwiseRelu2,
+                  "nemotron_b200 provides only the operators on the model's path: Add and Relu2");
+    (void)scale; (void)bias; (void)clamp_min; (void)clamp_max;
+    if (ops_type == kElementwiseAdd) nmt_add_bf16(in0, in1, out0, static_cast<int64_t>(size), stream);
+    else nmt_relu2_bf16(in0, out0, static_cast<int64_t>(size), stream);
+}
+
+}  // namespace nemotron::ops
+
+#endif  // NEMOTRON_B200_SHIM_ELEMENTWISE_CUH
