@@ -113,7 +113,11 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) >= 7:
-                self.samples.append(parts)
+                self.samples.append([time.perf_counter()] + parts)
+
+    def window(self, t0: float, t1: float) -> None:
+        """Keeps only the samples taken inside [t0, t1] (the timed region)."""
+        self.t0, self.t1 = t0, t1
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -127,7 +131,9 @@ class ClockSampler:
             self.thread.join(timeout=2)
         sm, mx, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        t0, t1 = getattr(self, "t0", None), getattr(self, "t1", None)
+        inside = [s[1:] for s in self.samples if t0 is None or (t0 <= s[0] <= t1 + 0.15)]
+        for s in inside or [s[1:] for s in self.samples[-3:]]:
             try:
                 sm.append(float(s[0]))
                 mx.append(float(s[1]))
@@ -242,20 +248,28 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> dict | None:
         cp.run()
     torch.cuda.synchronize()
 
+    # the sampler starts ahead of the timed region (nvidia-smi takes a moment to come up) and keeps the GPU
+    # busy meanwhile; only samples inside the timed window are reported
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    for _ in range(5):
+        cp.run()
     traced = TracedChain(cp)
     launches0 = ops.launch_count()
     barrier()
     torch.cuda.synchronize()
-    if sampler:
-        sampler.start()
+    t_start = time.perf_counter()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
         traced.run()
     ev1.record()
     torch.cuda.synchronize()
+    t_end = time.perf_counter()
     barrier()
+    if sampler:
+        sampler.window(t_start, t_end)
     clocks = sampler.stop() if sampler else None
     launches = ops.launch_count() - launches0
     ms_total = max_over_ranks(ev0.elapsed_time(ev1))
@@ -404,7 +418,7 @@ def run_reference_cuda(args, local_rank: int, quiet: bool = False) -> dict:
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference-cuda"])
     ap.add_argument("--tokens", type=int, default=TOKENS_PER_GPU, help="tokens per GPU (weak scaling)")
@@ -416,13 +430,21 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    # Libraries (NCCL's version banner, for one) write to stdout; keep stdout for the ONE JSON line.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj: dict) -> None:
+        os.write(json_fd, (json.dumps(obj) + "\n").encode())
+
     if args.impl == "reference":
         if rank == 0:
-            print(json.dumps(run_reference_cpu(args, world)), flush=True)
+            emit(run_reference_cpu(args, world))
         return
     if args.impl == "reference-cuda":
         if rank == 0:
-            print(json.dumps(run_reference_cuda(args, local_rank)), flush=True)
+            emit(run_reference_cuda(args, local_rank))
         return
 
     if world > 1:
@@ -432,7 +454,7 @@ def main() -> None:
     try:
         out = run_b200(args, rank, world, local_rank)
         if rank == 0 and out is not None:
-            print(json.dumps(out), flush=True)
+            emit(out)
     finally:
         if world > 1 and dist.is_initialized():
             dist.destroy_process_group()

@@ -124,6 +124,21 @@ class ChainPass:
         self.final_hidden = cur
         return b.normed
 
+    def capture(self) -> None:
+        """Records the 81-launch pass into a CUDA graph.  For decode-sized shards (T = 1 ... 64) the pass is
+        bound by launch overhead, not bandwidth: one graph launch replaces 81 host-side launches."""
+        self.run()                                   # warm-up outside the capture (one-time kernel attributes)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.run()
+        self.graph = graph
+
+    def replay(self) -> torch.Tensor:
+        """Replays the captured pass on the current stream; same buffers, same result as run()."""
+        self.graph.replay()
+        return self.buf.normed
+
     def run_from_host(self, ids_host: torch.Tensor) -> torch.Tensor:
         """The end-to-end call: token ids arrive in (pinned) host memory, the last token's normed hidden
         state comes back to host memory — what the engine's prefill hands to lm_head (engine.py:241-251)."""

@@ -40,6 +40,7 @@ __device__ __forceinline__ uint4 apply_op(const uint4& a, const uint4& b) {
 template <int OP, int U, int MAXB>
 __global__ void __launch_bounds__(MAXB)
 ew_stream_kernel(const uint4* a, const uint4* b, uint4* out, int64_t nv) {
+    pdl_wait();
     const int64_t tile_vecs = (int64_t)blockDim.x * U;
     for (int64_t base = (int64_t)blockIdx.x * tile_vecs; base < nv; base += (int64_t)gridDim.x * tile_vecs) {
         uint4 va[U], vb[U];
@@ -57,17 +58,20 @@ ew_stream_kernel(const uint4* a, const uint4* b, uint4* out, int64_t nv) {
             if (i < nv) st_stream(out + i, apply_op<OP>(va[u], vb[u]));
         }
     }
+    pdl_trigger();
 }
 
 // fp32 twins (parity only).  relu2 follows torch: NaN in, NaN out.
 template <int OP>
 __global__ void __launch_bounds__(256)
 ew_f32_kernel(const float* a, const float* b, float* out, int64_t n) {
+    pdl_wait();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const float x = a[i];
         if (OP == kOpRelu2) out[i] = x > 0.f ? x * x : (x == x ? 0.f : x);
         else out[i] = x + b[i];
     }
+    pdl_trigger();
 }
 
 template <int OP>
@@ -84,8 +88,8 @@ static int launch_ew_bf16(const void* a, const void* b, void* out, int64_t n, cu
 #define NMT_EW_CASE(U)                                                                              \
     do {                                                                                            \
         const int grid = grid_for(nv, block * U, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);      \
-        if (block <= 256) ew_stream_kernel<OP, U, 256><<<grid, block, 0, st>>>(A, B, O, nv);        \
-        else ew_stream_kernel<OP, U, 1024><<<grid, block, 0, st>>>(A, B, O, nv);                    \
+        if (block <= 256) launch_kernel(ew_stream_kernel<OP, U, 256>, grid, block, 0, st, A, B, O, nv);        \
+        else launch_kernel(ew_stream_kernel<OP, U, 1024>, grid, block, 0, st, A, B, O, nv);                    \
     } while (0)
     if (unroll >= 16) NMT_EW_CASE(16);
     else if (unroll >= 8) NMT_EW_CASE(8);
@@ -128,7 +132,7 @@ int nmt_relu2_f32(const float* u, float* out, int64_t n, void* stream) {
     int s = nmt::check_ew(u, nullptr, out, n, false, false);
     if (s != NMT_OK || n == 0) return s;
     const int grid = nmt::grid_for(n, 256 * 4, nmt::kSmCount * 16);
-    nmt::ew_f32_kernel<nmt::kOpRelu2><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(u, nullptr, out, n);
+    nmt::launch_kernel(nmt::ew_f32_kernel<nmt::kOpRelu2>, grid, 256, 0, static_cast<cudaStream_t>(stream), u, nullptr, out, n);
     return nmt::finish_launch(1);
 }
 
@@ -136,7 +140,7 @@ int nmt_add_f32(const float* a, const float* b, float* out, int64_t n, void* str
     int s = nmt::check_ew(a, b, out, n, true, false);
     if (s != NMT_OK || n == 0) return s;
     const int grid = nmt::grid_for(n, 256 * 4, nmt::kSmCount * 16);
-    nmt::ew_f32_kernel<nmt::kOpAdd><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(a, b, out, n);
+    nmt::launch_kernel(nmt::ew_f32_kernel<nmt::kOpAdd>, grid, 256, 0, static_cast<cudaStream_t>(stream), a, b, out, n);
     return nmt::finish_launch(1);
 }
 

@@ -12,6 +12,7 @@ template <int SLOTS, typename IdT>
 __global__ void __launch_bounds__(256)
 embedding_rowwarp_kernel(const uint4* __restrict__ table, const IdT* __restrict__ ids, uint4* __restrict__ out,
                          int64_t num_tokens, int nv, int64_t vocab, int32_t* err_flag) {
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
@@ -33,6 +34,7 @@ embedding_rowwarp_kernel(const uint4* __restrict__ table, const IdT* __restrict_
             if (i < nv) st_stream(out + t * nv + i, v[s]);
         }
     }
+    pdl_trigger();
 }
 
 // Any width: one warp per token, looped.
@@ -40,6 +42,7 @@ template <typename IdT>
 __global__ void __launch_bounds__(256)
 embedding_generic_kernel(const uint4* __restrict__ table, const IdT* __restrict__ ids, uint4* __restrict__ out,
                          int64_t num_tokens, int64_t nv, int64_t vocab, int32_t* err_flag) {
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
@@ -52,6 +55,7 @@ embedding_generic_kernel(const uint4* __restrict__ table, const IdT* __restrict_
         for (int64_t i = lane; i < nv; i += 32)
             st_stream(out + t * nv + i, ok ? ld_stream(src + i) : make_uint4(0, 0, 0, 0));
     }
+    pdl_trigger();
 }
 
 template <typename IdT>
@@ -86,12 +90,12 @@ static int launch_embedding(const void* table, const IdT* ids, void* out, int64_
     const int grid = grid_for(num_tokens, wpc, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);
     const int64_t slots = (nv + 31) / 32;
 #define NMT_EMB_CASE(S) \
-    embedding_rowwarp_kernel<S, IdT><<<grid, block, 0, st>>>(T, ids, O, num_tokens, (int)nv, vocab, err_flag)
+    launch_kernel(embedding_rowwarp_kernel<S, IdT>, grid, block, 0, st, T, ids, O, num_tokens, (int)nv, vocab, err_flag)
     if (slots <= 4) NMT_EMB_CASE(4);
     else if (slots <= 8) NMT_EMB_CASE(8);
     else if (slots <= 13) NMT_EMB_CASE(13);
     else if (slots <= 16) NMT_EMB_CASE(16);
-    else embedding_generic_kernel<IdT><<<grid, block, 0, st>>>(T, ids, O, num_tokens, nv, vocab, err_flag);
+    else launch_kernel(embedding_generic_kernel<IdT>, grid, block, 0, st, T, ids, O, num_tokens, nv, vocab, err_flag);
 #undef NMT_EMB_CASE
     return finish_launch(1);
 }

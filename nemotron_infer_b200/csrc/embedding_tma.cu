@@ -20,6 +20,7 @@ template <int STAGES, typename IdT>
 __global__ void __launch_bounds__(256)
 embedding_relay_kernel(const uint8_t* __restrict__ table, const IdT* __restrict__ ids, uint8_t* __restrict__ out,
                        int64_t num_tokens, uint32_t row_bytes, uint32_t slot_stride, int64_t vocab, int32_t* err_flag) {
+    pdl_wait();
     constexpr int LAG = STAGES / 2;
     extern __shared__ __align__(128) uint8_t smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -90,6 +91,7 @@ embedding_relay_kernel(const uint8_t* __restrict__ table, const IdT* __restrict_
     }
     // Shared memory must outlive every bulk store that reads it.
     if (lane == 0) bulk_wait_all<0>();
+    pdl_trigger();
 }
 
 template <int STAGES, typename IdT>
@@ -117,7 +119,7 @@ static int launch_relay(const void* table, const IdT* ids, void* out, int64_t nu
             return finish_launch(0);
         configured[dev] = true;
     }
-    kern<<<static_cast<int>(grid), warps * 32, smem, st>>>(static_cast<const uint8_t*>(table), ids,
+    launch_kernel(kern, static_cast<int>(grid), warps * 32, smem, st, static_cast<const uint8_t*>(table), ids,
                                                          static_cast<uint8_t*>(out), num_tokens, row_bytes,
                                                          slot_stride, vocab, err_flag);
     return finish_launch(1);

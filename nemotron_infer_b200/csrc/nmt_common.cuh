@@ -60,12 +60,57 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return v;
 }
 
+// ---------------------------------------------------------------------------
+// Packed forms.  sm_100 issues fp32 add / mul / fma on register PAIRS (add.rn.f32x2, mul.rn.f32x2,
+// fma.rn.f32x2: two IEEE round-to-nearest results per instruction), and bf16 pairs add natively
+// (add.bf16x2, one rounding of the exact sum).  Working on the (lo, hi) pair of each 32-bit word halves
+// the arithmetic instruction count of these bandwidth-bound kernels without changing a single result bit.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float2 unpack2(uint32_t u) { return make_float2(bf16_lo(u), bf16_hi(u)); }
+__device__ __forceinline__ uint32_t pack2(const float2& f) { return pack_bf16x2(f.x, f.y); }
+__device__ __forceinline__ void unpack8x2(const uint4& v, float2 (&p)[4]) {
+    p[0] = unpack2(v.x); p[1] = unpack2(v.y); p[2] = unpack2(v.z); p[3] = unpack2(v.w);
+}
+__device__ __forceinline__ uint4 pack8x2(const float2 (&p)[4]) {
+    return make_uint4(pack2(p[0]), pack2(p[1]), pack2(p[2]), pack2(p[3]));
+}
+__device__ __forceinline__ uint32_t add_bf16x2_rn(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("add.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint4 add_bf16x8_rn(const uint4& a, const uint4& b) {
+    return make_uint4(add_bf16x2_rn(a.x, b.x), add_bf16x2_rn(a.y, b.y), add_bf16x2_rn(a.z, b.z), add_bf16x2_rn(a.w, b.w));
+}
+// out = (p * rstd) * w for the eight elements of one vector, in that association order.
+__device__ __forceinline__ uint4 scale8(const float2 (&p)[4], float rstd, const float4& w0, const float4& w1) {
+    const float2 rs = make_float2(rstd, rstd);
+    float2 o[4];
+    o[0] = __fmul2_rn(__fmul2_rn(p[0], rs), make_float2(w0.x, w0.y));
+    o[1] = __fmul2_rn(__fmul2_rn(p[1], rs), make_float2(w0.z, w0.w));
+    o[2] = __fmul2_rn(__fmul2_rn(p[2], rs), make_float2(w1.x, w1.y));
+    o[3] = __fmul2_rn(__fmul2_rn(p[3], rs), make_float2(w1.z, w1.w));
+    return pack8x2(o);
+}
+
 // Butterfly sum: every lane ends with the warp total.
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel first waits until the PREVIOUS kernel in the stream has
+// completed and its writes are visible (pdl_wait, before any global access), and as its last act tells the
+// scheduler that the NEXT kernel may start launching (pdl_trigger), which hides that kernel's launch
+// latency behind this one's last CTAs.  The trigger sits at the END of a CTA's work on purpose: issued at
+// the start it let the next kernel's CTAs, parked in their wait, take SM slots from this kernel's own
+// not-yet-launched CTAs, and a chain of unlike kernels ran 20 % slower.  Without the launch attribute both
+// instructions are no-ops, so the kernels behave identically under a plain launch.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------
 // Host side
@@ -76,6 +121,24 @@ inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3
 extern std::atomic<int64_t> g_launches;
 int finish_launch(int n_kernels);   // records cudaGetLastError(); returns an nmt_status
 int tune(const char* key, int dflt);  // current value of a tuning knob
+
+bool pdl_enabled();   // runtime.cu: knob "launch.pdl"
+
+// One launch path for every kernel: plain, or with programmatic stream serialization when enabled.
+template <typename... KArgs, typename... Args>
+inline void launch_kernel(void (*kern)(KArgs...), int grid, int block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(block));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 
 inline int grid_for(int64_t work_items, int items_per_cta, int max_ctas) {
     int64_t g = (work_items + items_per_cta - 1) / items_per_cta;

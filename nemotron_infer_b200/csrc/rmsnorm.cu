@@ -17,6 +17,7 @@ __global__ void __launch_bounds__(256)
 rmsnorm_rowwarp_kernel(const uint4* x, const uint4* r,
                        const float* __restrict__ w, uint4* out_res, uint4* out,
                        int64_t rows, int nv, float inv_cols, float eps) {
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
@@ -75,74 +76,81 @@ rmsnorm_rowwarp_kernel(const uint4* x, const uint4* r,
             }
         }
     }
+    pdl_trigger();
 }
 
-// CTA-per-row register variant: blockDim threads share one row (thread t owns vectors t, t + blockDim, ...),
-// so each thread holds only SLOTS = ceil(vectors / blockDim) vectors of x and r.  Few registers per thread
-// means many resident warps (the occupancy the memory system needs), and the price is one block barrier
-// per row for the sum of squares.  Partial sums are added in a fixed order, so results are deterministic.
-template <int SLOTS, bool FUSE_ADD>
+// CTA-per-row register variant: blockDim threads share ROWS consecutive rows (thread t owns vectors t,
+// t + blockDim, ... of each), so each thread holds only SLOTS = ceil(vectors / blockDim) vectors of x and r per
+// row.  Few registers per thread means many resident warps (the occupancy the memory system needs), and the
+// price is one block barrier per row group for the sum of squares.  Partial sums are added in a fixed order,
+// so results are deterministic.  The arithmetic runs on register pairs (add.bf16x2 for the residual sum, which
+// rounds the exact sum once exactly like "add in fp32, round to bf16"; f32x2 fma / mul for the rest).
+template <int SLOTS, int ROWS, bool FUSE_ADD>
 __global__ void __launch_bounds__(512)
 rmsnorm_ctarow_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, uint4* out_res, uint4* out,
                       int64_t rows, int nv, float inv_cols, float eps) {
-    __shared__ __align__(16) float s_part[2][16];
+    pdl_wait();
+    __shared__ __align__(16) float s_part[2][ROWS][16];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     int flip = 0;
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, flip ^= 1) {
-        const uint4* xr = x + row * nv;
-        const uint4* rr = FUSE_ADD ? r + row * nv : nullptr;
-        uint4 a[SLOTS], b[SLOTS];
+    for (int64_t row0 = (int64_t)blockIdx.x * ROWS; row0 < rows; row0 += (int64_t)gridDim.x * ROWS, flip ^= 1) {
+        uint4 a[ROWS][SLOTS], b[ROWS][SLOTS];
 #pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            const int v = s * blockDim.x + threadIdx.x;
-            if (v < nv) {
-                a[s] = ld_stream(xr + v);
-                if (FUSE_ADD) b[s] = ld_stream(rr + v);
-            } else {
-                a[s] = make_uint4(0, 0, 0, 0);
-                if (FUSE_ADD) b[s] = make_uint4(0, 0, 0, 0);
-            }
-        }
-        float ss = 0.f;
+        for (int q = 0; q < ROWS; ++q) {
+            const int64_t row = row0 + q;
 #pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            float f[8];
-            unpack8(a[s], f);
-            if (FUSE_ADD) {
-                float g[8];
-                unpack8(b[s], g);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) f[k] += g[k];
-                a[s] = pack8(f);                    // round the residual stream before the norm sees it
-                unpack8(a[s], f);
+            for (int s = 0; s < SLOTS; ++s) {
                 const int v = s * blockDim.x + threadIdx.x;
-                if (v < nv) st_stream(out_res + row * nv + v, a[s]);
+                if (row < rows && v < nv) {
+                    a[q][s] = ld_stream(x + row * nv + v);
+                    if (FUSE_ADD) b[q][s] = ld_stream(r + row * nv + v);
+                } else {
+                    a[q][s] = make_uint4(0, 0, 0, 0);
+                    if (FUSE_ADD) b[q][s] = make_uint4(0, 0, 0, 0);
+                }
             }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) ss = fmaf(f[k], f[k], ss);
         }
-        ss = warp_sum(ss);
-        if (lane == 0) s_part[flip][wid] = ss;
-        __syncthreads();
-        float total = 0.f;
-        for (int i = 0; i < nwarps; ++i) total += s_part[flip][i];
-        const float rstd = rsqrtf(total * inv_cols + eps);
 #pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            const int v = s * blockDim.x + threadIdx.x;
-            if (v < nv) {
-                float f[8];
-                unpack8(a[s], f);
-                const float4 w0 = ld_weight4(w + v * 8);
-                const float4 w1 = ld_weight4(w + v * 8 + 4);
-                f[0] = (f[0] * rstd) * w0.x; f[1] = (f[1] * rstd) * w0.y;
-                f[2] = (f[2] * rstd) * w0.z; f[3] = (f[3] * rstd) * w0.w;
-                f[4] = (f[4] * rstd) * w1.x; f[5] = (f[5] * rstd) * w1.y;
-                f[6] = (f[6] * rstd) * w1.z; f[7] = (f[7] * rstd) * w1.w;
-                st_stream(out + row * nv + v, pack8(f));
+        for (int q = 0; q < ROWS; ++q) {
+            const int64_t row = row0 + q;
+            float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int s = 0; s < SLOTS; ++s) {
+                if (FUSE_ADD) {
+                    // The residual stream is rounded to bf16 first: the norm must see what the next block
+                    // would read back from memory.
+                    a[q][s] = add_bf16x8_rn(a[q][s], b[q][s]);
+                    const int v = s * blockDim.x + threadIdx.x;
+                    if (row < rows && v < nv) st_stream(out_res + row * nv + v, a[q][s]);
+                }
+                float2 p[4];
+                unpack8x2(a[q][s], p);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc = __ffma2_rn(p[k], p[k], acc);
+            }
+            const float ss = warp_sum(acc.x + acc.y);
+            if (lane == 0) s_part[flip][q][wid] = ss;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < ROWS; ++q) {
+            const int64_t row = row0 + q;
+            if (row >= rows) break;
+            float total = 0.f;
+            for (int i = 0; i < nwarps; ++i) total += s_part[flip][q][i];
+            const float rstd = rsqrtf(total * inv_cols + eps);
+#pragma unroll
+            for (int s = 0; s < SLOTS; ++s) {
+                const int v = s * blockDim.x + threadIdx.x;
+                if (v < nv) {
+                    float2 p[4];
+                    unpack8x2(a[q][s], p);
+                    st_stream(out + row * nv + v, scale8(p, rstd, ld_weight4(w + v * 8), ld_weight4(w + v * 8 + 4)));
+                }
             }
         }
     }
+    pdl_trigger();
 }
 
 // Any width: one CTA per row, two passes.  The second pass re-reads what the
@@ -153,6 +161,7 @@ __global__ void __launch_bounds__(256)
 rmsnorm_rowcta_kernel(const uint4* x, const uint4* r,
                       const float* __restrict__ w, uint4* out_res, uint4* out,
                       int64_t rows, int64_t nv, float inv_cols, float eps) {
+    pdl_wait();
     __shared__ float s_part[8];
     __shared__ float s_total;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -199,12 +208,14 @@ rmsnorm_rowcta_kernel(const uint4* x, const uint4* r,
         }
         __syncthreads();   // s_part / s_total are reused by the next row
     }
+    pdl_trigger();
 }
 
 // fp32 twin (parity only): one CTA per row, scalar, two passes.
 __global__ void __launch_bounds__(256)
 rmsnorm_f32_kernel(const float* __restrict__ x, float* y, const float* __restrict__ w,
                    int64_t rows, int64_t cols, float eps) {
+    pdl_wait();
     __shared__ float s_part[8];
     __shared__ float s_total;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -225,6 +236,7 @@ rmsnorm_f32_kernel(const float* __restrict__ x, float* y, const float* __restric
         for (int64_t c = threadIdx.x; c < cols; c += blockDim.x) y[row * cols + c] = (xr[c] * rstd) * w[c];
         __syncthreads();
     }
+    pdl_trigger();
 }
 
 int launch_norm_tma(bool fuse, const void* x, const void* r, const float* w, void* out_res, void* out,
@@ -254,9 +266,13 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
         block = block > 512 ? 512 : (block + 31) / 32 * 32;
         const int slots = static_cast<int>((nv + block - 1) / block);
         const int per_sm = tune("norm.ctas_per_sm", 0);
-        const int grid = grid_for(rows, 1, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);
-#define NMT_CTAROW_CASE(S) \
-    rmsnorm_ctarow_kernel<S, FUSE_ADD><<<grid, block, 0, st>>>(X, R, w, OR, O, rows, (int)nv, inv_cols, eps)
+        const int rows_per_cta = tune("norm.rows_per_cta", FUSE_ADD ? 1 : 2);
+        const int grid = grid_for(rows, rows_per_cta >= 2 ? 2 : 1, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);
+#define NMT_CTAROW_CASE(S)                                                                                   \
+    do {                                                                                                     \
+        if (rows_per_cta >= 2) launch_kernel(rmsnorm_ctarow_kernel<S, 2, FUSE_ADD>, grid, block, 0, st, X, R, w, OR, O, rows, (int)nv, inv_cols, eps); \
+        else launch_kernel(rmsnorm_ctarow_kernel<S, 1, FUSE_ADD>, grid, block, 0, st, X, R, w, OR, O, rows, (int)nv, inv_cols, eps);                   \
+    } while (0)
         if (slots <= 1) NMT_CTAROW_CASE(1);
         else if (slots <= 2) NMT_CTAROW_CASE(2);
         else if (slots <= 3) NMT_CTAROW_CASE(3);
@@ -271,7 +287,7 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
 wide:
     if (nv > 16 * 32) {
         const int grid = grid_for(rows, 1, kSmCount * 16);
-        rmsnorm_rowcta_kernel<FUSE_ADD><<<grid, 256, 0, st>>>(X, R, w, OR, O, rows, nv, inv_cols, eps);
+        launch_kernel(rmsnorm_rowcta_kernel<FUSE_ADD>, grid, 256, 0, st, X, R, w, OR, O, rows, nv, inv_cols, eps);
         return finish_launch(1);
     }
     int block = tune("norm.block", 64);      // warp-per-row variant
@@ -281,7 +297,7 @@ wide:
     const int grid = grid_for(rows, wpc, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);
     const int slots = static_cast<int>((nv + 31) / 32);
 #define NMT_NORM_CASE(S)                                                                           \
-    rmsnorm_rowwarp_kernel<S, FUSE_ADD><<<grid, block, 0, st>>>(X, R, w, OR, O, rows, (int)nv, inv_cols, eps)
+    launch_kernel(rmsnorm_rowwarp_kernel<S, FUSE_ADD>, grid, block, 0, st, X, R, w, OR, O, rows, (int)nv, inv_cols, eps)
     if (slots <= 2) NMT_NORM_CASE(2);
     else if (slots <= 4) NMT_NORM_CASE(4);
     else if (slots <= 8) NMT_NORM_CASE(8);
@@ -309,7 +325,7 @@ int nmt_rmsnorm_f32(const float* x, float* y, const float* w, int64_t rows, int6
     if (!x || !y || !w) return NMT_ERR_NULL;
     if (!nmt::aligned4(x) || !nmt::aligned4(y) || !nmt::aligned4(w)) return NMT_ERR_ALIGN;
     const int grid = nmt::grid_for(rows, 1, nmt::kSmCount * 8);
-    nmt::rmsnorm_f32_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(x, y, w, rows, cols, eps);
+    nmt::launch_kernel(nmt::rmsnorm_f32_kernel, grid, 256, 0, static_cast<cudaStream_t>(stream), x, y, w, rows, cols, eps);
     return nmt::finish_launch(1);
 }
 

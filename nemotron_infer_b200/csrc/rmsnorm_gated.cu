@@ -21,12 +21,24 @@ __device__ __forceinline__ float silu_sfu(float z) {
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(1.0f + e));
     return z * rcp;
 }
+// Two at a time: the multiplies and the add run as f32x2 instructions, the two SFU ops stay scalar.
+__device__ __forceinline__ float2 silu2_sfu(const float2& z) {
+    const float2 t = __fmul2_rn(z, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+    float2 e, rcp;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(t.x));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(t.y));
+    const float2 d = __fadd2_rn(e, make_float2(1.0f, 1.0f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp.x) : "f"(d.x));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp.y) : "f"(d.y));
+    return __fmul2_rn(z, rcp);
+}
 __device__ __forceinline__ float silu_exact(float z) { return z / (1.0f + expf(-z)); }
 
 template <int SLOTS, int RPI>
 __global__ void __launch_bounds__(256)
 gated_groupwarp_kernel(const uint4* y, const uint4* z, const float* __restrict__ w, uint4* out,
                        int64_t items, int groups, int gv, float inv_gs, float eps) {
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
@@ -55,38 +67,31 @@ gated_groupwarp_kernel(const uint4* y, const uint4* z, const float* __restrict__
             const int64_t it = it0 + q;
             if (it >= items) break;                       // warp-uniform
             const int grp = static_cast<int>(it % groups);
-            float g[SLOTS][8];
-            float ss = 0.f;
+            float2 g[SLOTS][4];
+            float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
             for (int s = 0; s < SLOTS; ++s) {
-                float fy[8], fz[8];
-                unpack8(a[q][s], fy);
-                unpack8(b[q][s], fz);
+                float2 py[4], pz[4];
+                unpack8x2(a[q][s], py);
+                unpack8x2(b[q][s], pz);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    g[s][k] = fy[k] * silu_sfu(fz[k]);
-                    ss = fmaf(g[s][k], g[s][k], ss);
+                for (int k = 0; k < 4; ++k) {
+                    g[s][k] = __fmul2_rn(py[k], silu2_sfu(pz[k]));
+                    acc = __ffma2_rn(g[s][k], g[s][k], acc);
                 }
             }
-            ss = warp_sum(ss);
+            const float ss = warp_sum(acc.x + acc.y);
             const float rstd = rsqrtf(ss * inv_gs + eps);
             const float* wg = w + (int64_t)grp * gv * 8;
 #pragma unroll
             for (int s = 0; s < SLOTS; ++s) {
                 const int v = s * 32 + lane;
-                if (v < gv) {
-                    const float4 w0 = ld_weight4(wg + v * 8);
-                    const float4 w1 = ld_weight4(wg + v * 8 + 4);
-                    float o[8];
-                    o[0] = (g[s][0] * rstd) * w0.x; o[1] = (g[s][1] * rstd) * w0.y;
-                    o[2] = (g[s][2] * rstd) * w0.z; o[3] = (g[s][3] * rstd) * w0.w;
-                    o[4] = (g[s][4] * rstd) * w1.x; o[5] = (g[s][5] * rstd) * w1.y;
-                    o[6] = (g[s][6] * rstd) * w1.z; o[7] = (g[s][7] * rstd) * w1.w;
-                    st_stream(out + it * gv + v, pack8(o));
-                }
+                if (v < gv)
+                    st_stream(out + it * gv + v, scale8(g[s], rstd, ld_weight4(wg + v * 8), ld_weight4(wg + v * 8 + 4)));
             }
         }
     }
+    pdl_trigger();
 }
 
 // Any group size (including sizes that are not a multiple of 8, or groups too
@@ -103,6 +108,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 gated_generic_kernel(const T* y, const T* z, const float* __restrict__ w, T* out,
                      int64_t items, int64_t groups, int64_t gs, float eps) {
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
@@ -123,6 +129,7 @@ gated_generic_kernel(const T* y, const T* z, const float* __restrict__ w, T* out
             out[it * gs + c] = from_f32<T>((g * rstd) * wg[c]);
         }
     }
+    pdl_trigger();
 }
 
 static int check_gated(const void* y, const void* z, const float* w, const void* out,
@@ -150,8 +157,7 @@ int nmt_rmsnorm_gated_bf16(const void* y, const void* z, const float* w, void* o
 
     if ((group_size % 8) != 0 || group_size / 8 > 8 * 32) {
         const int grid = grid_for(items, 8, kSmCount * 32);
-        gated_generic_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-            static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z), w,
+        launch_kernel(gated_generic_kernel<__nv_bfloat16>, grid, 256, 0, st, static_cast<const __nv_bfloat16*>(y), static_cast<const __nv_bfloat16*>(z), w,
             static_cast<__nv_bfloat16*>(out), items, groups, group_size, eps);
         return finish_launch(1);
     }
@@ -169,8 +175,8 @@ int nmt_rmsnorm_gated_bf16(const void* y, const void* z, const float* w, void* o
     auto O = static_cast<uint4*>(out);
 #define NMT_GATED_CASE(S)                                                                              \
     do {                                                                                               \
-        if (rpi >= 2) gated_groupwarp_kernel<S, 2><<<grid, block, 0, st>>>(Y, Z, w, O, items, (int)groups, gv, inv_gs, eps); \
-        else gated_groupwarp_kernel<S, 1><<<grid, block, 0, st>>>(Y, Z, w, O, items, (int)groups, gv, inv_gs, eps);          \
+        if (rpi >= 2) launch_kernel(gated_groupwarp_kernel<S, 2>, grid, block, 0, st, Y, Z, w, O, items, (int)groups, gv, inv_gs, eps); \
+        else launch_kernel(gated_groupwarp_kernel<S, 1>, grid, block, 0, st, Y, Z, w, O, items, (int)groups, gv, inv_gs, eps);          \
     } while (0)
     if (slots <= 1) NMT_GATED_CASE(1);
     else if (slots <= 2) NMT_GATED_CASE(2);
@@ -191,8 +197,7 @@ int nmt_rmsnorm_gated_f32(const float* y, const float* z, const float* w, float*
     const int64_t groups = cols / group_size;
     const int64_t items = rows * groups;
     const int grid = grid_for(items, 8, kSmCount * 32);
-    gated_generic_kernel<float><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        y, z, w, out, items, groups, group_size, eps);
+    launch_kernel(gated_generic_kernel<float>, grid, 256, 0, static_cast<cudaStream_t>(stream), y, z, w, out, items, groups, group_size, eps);
     return finish_launch(1);
 }
 

@@ -20,6 +20,7 @@ template <int SLOTS, bool FUSE_ADD>
 __global__ void __launch_bounds__(32 * 9)
 norm_tma_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, uint4* out_res, uint4* out,
                 int64_t rows, int nv, float inv_cols, float eps, int stages) {
+    pdl_wait();
     extern __shared__ __align__(128) uint8_t smem[];
     const int C = (blockDim.x >> 5) - 1;                 // consumer warps = rows per tile
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -120,6 +121,7 @@ norm_tma_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, uin
             if (lane == 0) mbar_arrive(empty + s);
         }
     }
+    pdl_trigger();
 }
 
 template <int SLOTS, bool FUSE_ADD>
@@ -134,7 +136,7 @@ static int launch_one(const uint4* X, const uint4* R, const float* w, uint4* OR,
             return finish_launch(0);
         configured[dev] = true;
     }
-    kern<<<grid, 32 * (C + 1), smem, st>>>(X, R, w, OR, O, rows, nv, inv_cols, eps, stages);
+    launch_kernel(kern, grid, 32 * (C + 1), smem, st, X, R, w, OR, O, rows, nv, inv_cols, eps, stages);
     return finish_launch(1);
 }
 

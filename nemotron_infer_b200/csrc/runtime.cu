@@ -22,10 +22,12 @@ int finish_launch(int n_kernels) {
 // Knobs are plain ints read at launch time.  0 means "let the launcher decide".
 struct Knob { const char* key; std::atomic<int> value; };
 static Knob g_knobs[] = {
+    {"launch.pdl", {0}},          // 1 = launch with programmatic stream serialization (default), 2 = plain launches
     // add_rmsnorm / rmsnorm (bf16)
     {"norm.variant", {0}},        // 0 = default (3), 1 = warp-per-row registers, 2 = TMA-staged tiles, 3 = CTA-per-row registers
     {"norm.block", {0}},          // threads per CTA for the warp-per-row kernel
     {"norm.ctas_per_sm", {0}},    // >0: persistent grid of 148*k CTAs; 0: one pass, grid = rows/warps
+    {"norm.rows_per_cta", {0}},   // CTA-per-row variant: rows a CTA loads together (1 or 2)
     {"norm.tma_rows", {0}},       // rows per TMA stage
     {"norm.tma_stages", {0}},
     // gated rmsnorm (bf16)
@@ -68,6 +70,8 @@ int64_t read_wait_timeouts() {
     }
     return total;
 }
+
+bool pdl_enabled() { return g_knobs[0].value.load(std::memory_order_relaxed) != 2; }
 
 int tune(const char* key, int dflt) {
     Knob* k = find_knob(key);

@@ -1,13 +1,15 @@
 """Per-op timing of the hot-path kernels at the benchmark shapes (the counterpart of the reference's
 in-test perf fixtures, tests/ops/test_reduce.cu:362-463, test_elementwise.cu:534-701, test_embedding.cu:196-221).
 
-    python -m nemotron_infer_b200.microbench [--op all|add_rmsnorm|rmsnorm|gated|gated_model|relu2|add|embedding]
+    python -m nemotron_infer_b200.microbench [--op all|add_rmsnorm|rmsnorm|gated|gated_model|relu2|add|embedding|chain]
                                              [--tokens T] [--reps R] [--warmup W] [--tune key=value ...]
 
 Each op runs on buffer sets that are rotated so that consecutive launches never touch the same bytes and
-the sets together exceed twice the 126 MB L2; every launch is bracketed by CUDA events on the launching
-stream.  One JSON line per op: median / min microseconds, algorithmic GB/s, tokens/s, and the fraction of
-the nominal 8000 GB/s and of the measured copy peak.
+the sets together exceed twice the 126 MB L2.  Timing is by CUDA events on the launching stream around
+BATCHES of back-to-back launches (--batch, default 10), so a figure includes the launch gaps a real
+sequence of kernels has but not the cost of an event record between every two launches.  One JSON line
+per op: median / min microseconds per launch, algorithmic GB/s, tokens/s, and the fraction of the nominal
+8000 GB/s and of the measured copy peak.
 """
 from __future__ import annotations
 
@@ -74,7 +76,7 @@ def make_case(op: str, T: int, dev):
     raise ValueError(op)
 
 
-def run_op(op: str, T: int, reps: int, warmup: int, dev) -> dict:
+def run_op(op: str, T: int, reps: int, warmup: int, dev, batch: int = 10) -> dict:
     _, bpt = SHAPES[op]
     nbytes = bpt * T
     nsets = max(2, min(8, -(-2 * L2_BYTES // max(nbytes, 1)) + 1))
@@ -84,19 +86,45 @@ def run_op(op: str, T: int, reps: int, warmup: int, dev) -> dict:
     torch.cuda.synchronize()
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
     evs[0].record()
+    n = 0
     for i in range(reps):
-        fns[i % nsets]()
+        for _ in range(batch):
+            fns[n % nsets]()
+            n += 1
         evs[i + 1].record()
     torch.cuda.synchronize()
-    us = sorted(evs[i].elapsed_time(evs[i + 1]) * 1e3 for i in range(reps))
+    us = sorted(evs[i].elapsed_time(evs[i + 1]) * 1e3 / batch for i in range(reps))
     med, mn = statistics.median(us), us[0]
     peak = measured_peak()
     gbs = nbytes / med / 1e3
-    return {"op": op, "tokens": T, "bytes_per_token": bpt, "buffer_sets": nsets, "reps": reps,
+    return {"op": op, "tokens": T, "bytes_per_token": bpt, "buffer_sets": nsets, "reps": reps, "batch": batch,
             "median_us": round(med, 2), "min_us": round(mn, 2), "gbs": round(gbs, 1),
             "gbs_best": round(nbytes / mn / 1e3, 1), "tokens_per_s": round(T / med * 1e6, 0),
             "frac_of_nominal_8000": round(gbs / NOMINAL_GBS, 4),
             "frac_of_measured_peak": round(gbs / peak, 4) if peak else None}
+
+
+def run_chain(T: int, reps: int, dev) -> dict:
+    """Latency of the whole 81-launch pass at a (small) token count: host-launched vs one CUDA-graph replay."""
+    from . import chain
+    cp = chain.ChainPass(T, dev, vocab=chain.VOCAB if T >= 4096 else 8192)
+    out = {"op": "chain", "tokens": T, "launches_per_pass": cp.launches_per_pass}
+    cp.capture()
+    for name, fn in (("eager", cp.run), ("graph", cp.replay)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        out[f"{name}_us_per_pass"] = round(us, 1)
+        out[f"{name}_tokens_per_s"] = round(T / us * 1e6, 0)
+        out[f"{name}_gbs"] = round(chain.bytes_per_token(4) * T / us / 1e3, 1)
+    return out
 
 
 def main() -> None:
@@ -105,6 +133,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=0, help="0 = the benchmark configuration's token count")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=10, help="back-to-back launches per timed interval")
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--tune", action="append", default=[], metavar="key=value")
     a = ap.parse_args()
@@ -115,8 +144,11 @@ def main() -> None:
         ops.tune(k, int(v))
     names = list(SHAPES) if a.op == "all" else a.op.split(",")
     for op in names:
+        if op == "chain":
+            print(json.dumps(run_chain(a.tokens or 64, a.reps, f"cuda:{a.device}")), flush=True)
+            continue
         T = a.tokens or SHAPES[op][0]
-        print(json.dumps(run_op(op, T, a.reps, a.warmup, f"cuda:{a.device}")), flush=True)
+        print(json.dumps(run_op(op, T, a.reps, a.warmup, f"cuda:{a.device}", a.batch)), flush=True)
         torch.cuda.empty_cache()
 
 

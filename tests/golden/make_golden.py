@@ -11,7 +11,7 @@ Two sources, neither of which copies reference text into this repository:
    write next to themselves and the mounted reference is read-only).  From their
    raw float32 dumps we keep the stage tensors that pin the hot-path ops:
      mlp:   input, block_norm_w -> normed (RMSNorm);  up -> act (relu^2);
-            input + down -> expected (residual add)
+            input + down -> expected (residual add); up_proj_w / down_proj_w for the whole-block check
      mamba: input, block_norm_w -> normed;  scan_y, gate, gnorm_w -> gnormed (gated RMSNorm)
 2. The functions `plain_rmsnorm` and `gated_rmsnorm` are lifted out of
    tools/dump_mamba_block.py with `ast` at run time and evaluated on the seeded
@@ -78,7 +78,7 @@ def main() -> None:
     torch.set_num_threads(1)          # fixed summation order for the fixtures
 
     mlp = run_dump(a.reference, "dump_mlp_block.py", "mlp_block")
-    keep = ["input", "block_norm_w", "normed", "up", "act", "down", "expected", "meta"]
+    keep = ["input", "block_norm_w", "up_proj_w", "down_proj_w", "normed", "up", "act", "down", "expected", "meta"]
     np.savez_compressed(os.path.join(HERE, "dump_mlp_block.npz"), **{k: mlp[k] for k in keep})
 
     mam = run_dump(a.reference, "dump_mamba_block.py", "mamba_block")

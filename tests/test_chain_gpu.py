@@ -52,6 +52,29 @@ def test_chain_pass_matches_oracle(built_lib, T):
     assert og.ulp_report(out, want_normed[T - 1])["max_ulp"] <= 1
 
 
+def test_graph_replay_equals_eager_pass(built_lib):
+    """The captured CUDA graph of the pass (decode-sized shard) reproduces the host-launched pass bit for bit,
+    with programmatic dependent launch on or off."""
+    from nemotron_infer_b200 import chain, ops
+    for T in (1, 64):
+        cp = chain.ChainPass(T, "cuda", vocab=4096, seed=T)
+        ref = cp.run().clone()
+        ref_hidden = cp.final_hidden.clone()
+        try:
+            for pdl in (2, 1):                      # 2 = plain launches, 1 = programmatic dependent launch
+                ops.tune("launch.pdl", pdl)
+                assert torch.equal(cp.run().view(torch.int16), ref.view(torch.int16))
+                cp.capture()
+                cp.buf.normed.zero_()
+                got = cp.replay()
+                torch.cuda.synchronize()
+                assert torch.equal(got.view(torch.int16), ref.view(torch.int16))
+                assert torch.equal(cp.final_hidden.view(torch.int16), ref_hidden.view(torch.int16))
+        finally:
+            ops.tune("launch.pdl", 0)
+    assert built_lib.nmt_device_wait_timeouts() == 0
+
+
 def test_sharded_chain_equals_unsharded(built_lib):
     """Token sharding: running rows [lo, hi) alone gives exactly the rows of the full run (no cross-row term)."""
     from nemotron_infer_b200 import chain
