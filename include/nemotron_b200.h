@@ -138,6 +138,36 @@ int nmt_embedding_bf16_i32(const void* table, const int32_t* ids, void* out,
                            int64_t num_tokens, int64_t hidden, int64_t vocab,
                            int32_t* err_flag, void* stream);
 
+/* ---- Per-tensor FP8 (e4m3) activation quantisation ---------------------------- */
+
+/* out_fp8 = e4m3(clamp(x / s, +-448)), s = max|x| / 448 (1/448 for an all-zero tensor), *scale_out = s.
+ * Replaces nemotron::ops::quantize_activation_fp8 (ops/gemm.cuh:291-307: fp8_amax_kernel :257-273 and
+ * fp8_quant_kernel :275-289), same arguments: `amax_scratch` is one device uint32 the call clears and uses.
+ * n % 8 == 0; x 16-byte, out 8-byte aligned.  scale_out may be NULL. */
+int nmt_quantize_fp8(const void* x_bf16, void* out_fp8, float* scale_out, unsigned int* amax_scratch,
+                     int64_t n, void* stream);
+
+/* relu^2 fused with the quantisation that follows it in the FP8 MLP block (model/mlp_block.cuh:163-168):
+ * out_fp8 = quantize(bf16(max(u,0)^2)) without ever writing the bf16 activation tensor. */
+int nmt_relu2_quant_fp8(const void* u_bf16, void* out_fp8, float* scale_out, unsigned int* amax_scratch,
+                        int64_t n, void* stream);
+
+/* Device workspace the two entry points below need for `rows` rows (one uint32 for the running maximum
+ * plus one float per row for its rstd); 16-byte aligned, caller-owned, contents need no initialisation. */
+int64_t nmt_fp8_workspace_bytes(int64_t rows);
+
+/* RMSNorm fused with the quantisation of its output (model/mlp_block.cuh:140,158; mamba_block.cuh:378-381;
+ * attention_block.cuh:328-330): out_fp8 = quantize(rmsnorm_bf16(x, w)), the bf16 normed tensor is never
+ * materialised.  cols % 8 == 0, cols <= 32768. */
+int nmt_rmsnorm_quant_fp8(const void* x, const float* w, void* out_fp8, float* scale_out, void* workspace,
+                          int64_t rows, int64_t cols, float eps, void* stream);
+
+/* The same with the preceding residual add: out_res = bf16(x + r), out_fp8 = quantize(rmsnorm_bf16(out_res, w)).
+ * out_res may alias x or r. */
+int nmt_add_rmsnorm_quant_fp8(const void* x, const void* r, const float* w, void* out_res, void* out_fp8,
+                              float* scale_out, void* workspace, int64_t rows, int64_t cols, float eps,
+                              void* stream);
+
 /* ---- Test and tuning hooks -------------------------------------------------- */
 
 /* Selects a kernel variant / launch shape by name (for measurement sweeps).

@@ -13,15 +13,6 @@ namespace nmt {
 
 enum { kOpRelu2 = 0, kOpAdd = 1 };
 
-__device__ __forceinline__ uint32_t relu2_bf16x2(uint32_t u) {
-    // fma.rn.relu.bf16x2 (x * 1 + 0, clamped at zero): one FMA-pipe instruction per pair; NaN stays NaN
-    // and -0 becomes +0.  The reference uses the same instruction (ops/elementwise.cuh:256-268).
-    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&u);
-    const __nv_bfloat162 one = __float2bfloat162_rn(1.f), zero = __float2bfloat162_rn(0.f);
-    x = __hfma2_relu(x, one, zero);
-    x = __hmul2(x, x);
-    return *reinterpret_cast<uint32_t*>(&x);
-}
 __device__ __forceinline__ uint32_t add_bf16x2(uint32_t a, uint32_t b) {
     __nv_bfloat162 r = __hadd2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
     return *reinterpret_cast<uint32_t*>(&r);

@@ -82,6 +82,15 @@ __device__ __forceinline__ uint32_t add_bf16x2_rn(uint32_t a, uint32_t b) {
 __device__ __forceinline__ uint4 add_bf16x8_rn(const uint4& a, const uint4& b) {
     return make_uint4(add_bf16x2_rn(a.x, b.x), add_bf16x2_rn(a.y, b.y), add_bf16x2_rn(a.z, b.z), add_bf16x2_rn(a.w, b.w));
 }
+__device__ __forceinline__ uint32_t relu2_bf16x2(uint32_t u) {
+    // fma.rn.relu.bf16x2 (x * 1 + 0, clamped at zero): one FMA-pipe instruction per pair; NaN stays NaN
+    // and -0 becomes +0.  The reference uses the same instruction (ops/elementwise.cuh:256-268).
+    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&u);
+    const __nv_bfloat162 one = __float2bfloat162_rn(1.f), zero = __float2bfloat162_rn(0.f);
+    x = __hfma2_relu(x, one, zero);
+    x = __hmul2(x, x);
+    return *reinterpret_cast<uint32_t*>(&x);
+}
 // out = (p * rstd) * w for the eight elements of one vector, in that association order.
 __device__ __forceinline__ uint4 scale8(const float2 (&p)[4], float rstd, const float4& w0, const float4& w1) {
     const float2 rs = make_float2(rstd, rstd);

@@ -260,7 +260,8 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
         // Default shape: about 160 threads per row (392 vectors -> 3 per thread), at most 8 vectors per thread.
         int block = tune("norm.block", 0);
         if (block <= 0) {
-            const int want_slots = static_cast<int>((nv + 159) / 160);
+            int want_slots = static_cast<int>((nv + 159) / 160);
+            if (want_slots > 8) want_slots = 8;
             block = static_cast<int>((nv + want_slots - 1) / want_slots);
         }
         block = block > 512 ? 512 : (block + 31) / 32 * 32;

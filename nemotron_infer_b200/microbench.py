@@ -35,6 +35,10 @@ SHAPES = {
     "relu2": (8192, 2 * 12544 * 2),
     "add": (8192, 3 * 3136 * 2),
     "embedding": (65536, 2 * 3136 * 2 + 4),
+    # e4m3 activation quantisation (the step after the norm / activation in the FP8 blocks)
+    "quantize_fp8": (8192, 3136 * (2 + 2 + 1)),                  # amax pass + quantising pass over [T, 3136]
+    "add_rmsnorm_quant_fp8": (8192, 3136 * (2 + 2 + 2 + 2 + 1)),  # x, r -> out_res ; out_res -> e4m3
+    "relu2_quant_fp8": (8192, 12544 * (2 + 2 + 1)),              # u twice in, e4m3 out
 }
 
 
@@ -67,6 +71,21 @@ def make_case(op: str, T: int, dev):
         u = (2 * rn(T, 12544)).to(BF)
         o = torch.empty_like(u)
         return lambda: ops.relu2(u, out=o)
+    if op == "quantize_fp8":
+        x = rn(T, 3136).to(BF)
+        q = torch.empty(T, 3136, dtype=torch.float8_e4m3fn, device=dev)
+        return lambda: ops.quantize_fp8(x, out=q)
+    if op == "relu2_quant_fp8":
+        u = (2 * rn(T, 12544)).to(BF)
+        q = torch.empty(T, 12544, dtype=torch.float8_e4m3fn, device=dev)
+        return lambda: ops.quantize_fp8(u, out=q, relu2_first=True)
+    if op == "add_rmsnorm_quant_fp8":
+        x, r = rn(T, 3136).to(BF), rn(T, 3136).to(BF)
+        w = 1 + 0.1 * rn(3136)
+        o1 = torch.empty_like(x)
+        q = torch.empty(T, 3136, dtype=torch.float8_e4m3fn, device=dev)
+        ws = ops.fp8_workspace(T, dev)
+        return lambda: ops.rmsnorm_quant_fp8(x, w, r=r, out_res=o1, out=q, workspace=ws)
     if op == "embedding":
         table = make_case.table if getattr(make_case, "table", None) is not None else (0.02 * rn(131072, 3136)).to(BF)
         make_case.table = table

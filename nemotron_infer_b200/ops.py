@@ -151,6 +151,60 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None =
     return out
 
 
+def _fp8_out(like: torch.Tensor, out: torch.Tensor | None) -> torch.Tensor:
+    out = torch.empty(like.shape, dtype=torch.float8_e4m3fn, device=like.device) if out is None else out
+    if out.dtype != torch.float8_e4m3fn or out.shape != like.shape:
+        raise ValueError("out must be float8_e4m3fn with the input's shape")
+    return out
+
+
+def quantize_fp8(x: torch.Tensor, out: torch.Tensor | None = None, relu2_first: bool = False):
+    """(q, scale): per-tensor dynamic e4m3 quantisation, q = e4m3(clamp(x / scale)), scale = max|x| / 448.
+    With relu2_first the tensor quantised is relu(x)^2, which is never written out."""
+    out = _fp8_out(x, out)
+    _dev(x, out)
+    if x.dtype != torch.bfloat16:
+        raise ValueError("x must be bf16")
+    scale = torch.empty(1, dtype=torch.float32, device=x.device)
+    amax = torch.empty(1, dtype=torch.int32, device=x.device)
+    lib = _lib.load()
+    fn = lib.nmt_relu2_quant_fp8 if relu2_first else lib.nmt_quantize_fp8
+    _lib.check(fn(x.data_ptr(), out.data_ptr(), scale.data_ptr(), amax.data_ptr(), x.numel(), _stream()), "quantize_fp8")
+    return out, scale
+
+
+def fp8_workspace(rows: int, device) -> torch.Tensor:
+    """Workspace for rmsnorm_quant_fp8 / add_rmsnorm_quant_fp8 on `rows` rows."""
+    return torch.empty(int(_lib.load().nmt_fp8_workspace_bytes(rows)), dtype=torch.uint8, device=device)
+
+
+def rmsnorm_quant_fp8(x: torch.Tensor, w: torch.Tensor, r: torch.Tensor | None = None, eps: float = EPS,
+                      out_res: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                      workspace: torch.Tensor | None = None):
+    """(q, scale) or, with a residual r, (out_res, q, scale): RMSNorm (after the residual add) fused with the
+    per-tensor e4m3 quantisation of its output; the bf16 normed tensor is never written."""
+    out = _fp8_out(x, out)
+    rows, cols = _rows_cols(x)
+    workspace = fp8_workspace(rows, x.device) if workspace is None else workspace
+    _dev(x, w, out, workspace)
+    if x.dtype != torch.bfloat16 or w.dtype != torch.float32 or w.numel() != cols:
+        raise ValueError("x must be bf16 and w fp32 with one entry per column")
+    scale = torch.empty(1, dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    if r is None:
+        _lib.check(lib.nmt_rmsnorm_quant_fp8(x.data_ptr(), w.data_ptr(), out.data_ptr(), scale.data_ptr(),
+                                             workspace.data_ptr(), rows, cols, eps, _stream()), "rmsnorm_quant_fp8")
+        return out, scale
+    out_res = torch.empty_like(x) if out_res is None else out_res
+    _dev(r, out_res)
+    if r.dtype != x.dtype or r.shape != x.shape or out_res.dtype != x.dtype or out_res.shape != x.shape:
+        raise ValueError("r and out_res must match x")
+    _lib.check(lib.nmt_add_rmsnorm_quant_fp8(x.data_ptr(), r.data_ptr(), w.data_ptr(), out_res.data_ptr(), out.data_ptr(),
+                                             scale.data_ptr(), workspace.data_ptr(), rows, cols, eps, _stream()),
+               "add_rmsnorm_quant_fp8")
+    return out_res, out, scale
+
+
 def tune(key: str, value: int) -> None:
     """Sets a launch-shape / variant knob (see nmt_tune_set in include/nemotron_b200.h)."""
     _lib.check(_lib.load().nmt_tune_set(key.encode(), int(value)), f"tune({key})")

@@ -36,6 +36,12 @@ BLK_API int blk_mlp_forward_bf16(const void* in, const float* norm_w, const void
     return static_cast<int>(cudaGetLastError());
 }
 
+// The reference's own activation quantiser (ops/gemm.cuh:291-307), for bit-level comparison.
+BLK_API int blk_quantize_activation_fp8(const void* x, void* out, float* scale, unsigned int* amax, size_t n) {
+    nemotron::ops::quantize_activation_fp8(static_cast<const bf16*>(x), static_cast<__nv_fp8_e4m3*>(out), scale, amax, n, nullptr);
+    return static_cast<int>(cudaGetLastError());
+}
+
 // The block's workspaces come from the reference's bump allocator; callers rewind it between calls
 // exactly as engine.py does through binding.reset_allocator() (binding.cu:59).
 BLK_API void blk_reset_allocator() { default_allocator().rewind(); }

@@ -84,6 +84,28 @@ def relu2_bf16(u: torch.Tensor) -> torch.Tensor:
     return relu2(u).to(torch.bfloat16)
 
 
+# --- per-tensor e4m3 quantisation of a bf16 activation tensor -----------------------
+# Restates fp8_amax_kernel + fp8_quant_kernel (ops/gemm.cuh:257-289): amax = max|x| over the bf16 tensor,
+# s = amax / 448 (1/448 when s < 1e-10), q = e4m3(clamp(x * (1/s), -448, 448)), all in fp32.
+
+def quantize_fp8(x: torch.Tensor):
+    assert x.dtype == torch.bfloat16
+    xf = x.float()
+    amax = xf.abs().max() if xf.numel() else torch.zeros(())
+    s = (amax / torch.tensor(448.0)).to(torch.float32)
+    if float(s) < 1e-10:
+        s = torch.tensor(1.0 / 448.0, dtype=torch.float32)
+    inv = (torch.tensor(1.0, dtype=torch.float32) / s).to(torch.float32)
+    q = torch.clamp(xf * inv, -448.0, 448.0).to(torch.float8_e4m3fn)
+    return q, s
+
+
+def e4m3_ordered(t: torch.Tensor) -> torch.Tensor:
+    bits = t.contiguous().view(torch.uint8).to(torch.int32)
+    mag = bits & 0x7F
+    return torch.where((bits & 0x80) != 0, -mag, mag)
+
+
 # --- comparison helpers ----------------------------------------------------------
 
 def bf16_ordered(t: torch.Tensor) -> torch.Tensor:
