@@ -38,7 +38,8 @@ typedef enum nmt_status {
     NMT_ERR_ALIGN = 2,       /* a pointer is not aligned as the contract requires */
     NMT_ERR_SHAPE = 3,       /* negative size, cols % 8 != 0, bad group size ...  */
     NMT_ERR_LAUNCH = 4,      /* the CUDA runtime refused the launch               */
-    NMT_ERR_UNSUPPORTED = 5  /* shape outside what the kernels cover              */
+    NMT_ERR_UNSUPPORTED = 5, /* shape outside what the kernels cover              */
+    NMT_ERR_TOO_LARGE = 6    /* more rows than the built-in scratch of a *_static entry point holds */
 } nmt_status;
 
 /* Library identity and status text. */
@@ -167,6 +168,29 @@ int nmt_rmsnorm_quant_fp8(const void* x, const float* w, void* out_fp8, float* s
 int nmt_add_rmsnorm_quant_fp8(const void* x, const void* r, const float* w, void* out_res, void* out_fp8,
                               float* scale_out, void* workspace, int64_t rows, int64_t cols, float eps,
                               void* stream);
+
+/* nmt_add_rmsnorm_quant_fp8 for callers that cannot provide the workspace.  This entry point has no
+ * counterpart in the reference.
+ *
+ * Who needs it: a host that must not, or cannot, allocate device memory at the point of the call -- the
+ * reference's engine bans cudaMalloc/cudaFree inside its per-layer loop because cudaFree stalls the device
+ * (ops/gemm.cuh:322-323, binding.cu:58); a minimal foreign-function binding only relays the tensor addresses it is given and
+ * has no device allocator; a server that has already committed all free memory to its caches cannot rely on a
+ * late allocation succeeding.  Here the workspace is a fixed array inside the library image instead.
+ *
+ * Same arguments and results as nmt_add_rmsnorm_quant_fp8 minus `workspace`; the call performs no allocation
+ * of any kind (host or device).  Limits and rules:
+ *   - rows <= NMT_STATIC_SCRATCH_MAX_ROWS, else NMT_ERR_TOO_LARGE is returned and nothing is launched.  The
+ *     array is 256 + 4 * NMT_STATIC_SCRATCH_MAX_ROWS bytes and is resident on every GPU that loads the library
+ *     for the life of the process.
+ *   - The first call on each device looks up the array's device address (with that device current) and caches
+ *     it; make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  Calls are safe back to back on one stream (each call resets
+ *     what it needs); two calls whose kernels can overlap on the GPU (different streams, no ordering between
+ *     them) race on the array and give wrong results -- order them, or use the workspace form for one. */
+#define NMT_STATIC_SCRATCH_MAX_ROWS 65536
+int nmt_add_rmsnorm_quant_fp8_static(const void* x, const void* r, const float* w, void* out_res, void* out_fp8,
+                                     float* scale_out, int64_t rows, int64_t cols, float eps, void* stream);
 
 /* ---- Test and tuning hooks -------------------------------------------------- */
 

@@ -280,9 +280,61 @@ static int launch_norm_quant(const void* x, const void* r, const float* w, void*
     return finish_launch(2);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Built-in scratch for nmt_add_rmsnorm_quant_fp8_static.
+//
+// The fused norm + quantise pair needs a little device memory between its two kernels: one word for the
+// running maximum and one float per row.  Some hosts have nowhere to get it from.  The reference's own
+// engine is one: it forbids cudaMalloc / cudaFree anywhere inside the per-layer loop (cudaFree stalls the
+// whole device, ops/gemm.cuh:322-323, binding.cu:58) and its bump allocator may have no slab left to carve from.  A thin
+// ctypes / cgo style binding is another: it only ever sees the tensor addresses the engine hands it and owns
+// no device allocator at all.  And a serving process that has given every free byte to its KV cache cannot
+// count on a late cudaMalloc to succeed.  For those callers the scratch lives inside the library image:
+// this array is part of the module, so it exists (on every GPU that loads the library, until the process
+// exits) without anyone allocating it.
+//
+// kStaticMaxRows bounds it: 256 bytes of header plus 4 bytes per row = 262,400 bytes per GPU.
+// ---------------------------------------------------------------------------------------------
+constexpr int64_t kStaticMaxRows = NMT_STATIC_SCRATCH_MAX_ROWS;
+static __device__ __align__(256) unsigned char g_fp8_static_scratch[256 + 4 * kStaticMaxRows];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel could use; the
+// device address has to be asked for, per device, with that device current.  It is looked up once per device
+// and remembered.
+static void* static_scratch_address(int* status) {
+    static void* per_device[64] = {};
+    static std::atomic<int> lock{0};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { *status = finish_launch(0); if (*status == NMT_OK) *status = NMT_ERR_LAUNCH; return nullptr; }
+    while (lock.exchange(1, std::memory_order_acquire)) {}
+    void* p = per_device[dev];
+    if (!p) {
+        void* sym = nullptr;
+        if (cudaGetSymbolAddress(&sym, g_fp8_static_scratch) == cudaSuccess && sym) per_device[dev] = p = sym;
+    }
+    lock.store(0, std::memory_order_release);
+    if (!p) { *status = finish_launch(0); if (*status == NMT_OK) *status = NMT_ERR_LAUNCH; return nullptr; }
+    *status = NMT_OK;
+    return p;
+}
+
 }  // namespace nmt
 
 extern "C" {
+
+int nmt_add_rmsnorm_quant_fp8_static(const void* x, const void* r, const float* w, void* out_res, void* out_fp8,
+                                     float* scale_out, int64_t rows, int64_t cols, float eps, void* stream) {
+    if (rows > nmt::kStaticMaxRows) return NMT_ERR_TOO_LARGE;     // would not fit the built-in scratch: nothing is launched
+    int status = NMT_OK;
+    void* scratch = nmt::static_scratch_address(&status);
+    if (!scratch) return status;
+    // Same two kernels as nmt_add_rmsnorm_quant_fp8, with the built-in array as their workspace.  The launcher
+    // zeroes the running-maximum word on the stream before the first kernel; the per-row floats are fully
+    // rewritten by the first kernel before the second reads them, so stale contents from an earlier call are
+    // never observed.
+    return nmt::launch_norm_quant<true>(x, r, w, out_res, out_fp8, scale_out, scratch, rows, cols, eps,
+                                        static_cast<cudaStream_t>(stream));
+}
 
 int64_t nmt_fp8_workspace_bytes(int64_t rows) {
     if (rows < 0) return -1;

@@ -94,6 +94,7 @@ const char* nmt_status_string(int s) {
         case NMT_ERR_SHAPE: return "bad shape (negative size, cols % 8 != 0, or group size does not divide cols)";
         case NMT_ERR_LAUNCH: return "CUDA launch failed (see nmt_last_cuda_error)";
         case NMT_ERR_UNSUPPORTED: return "unsupported shape or unknown tuning key";
+        case NMT_ERR_TOO_LARGE: return "rows exceed NMT_STATIC_SCRATCH_MAX_ROWS, the capacity of the built-in scratch; use the workspace form";
         default: return "unknown status";
     }
 }
