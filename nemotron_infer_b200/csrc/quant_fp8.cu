@@ -186,7 +186,7 @@ norm_stats_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, u
     pdl_trigger();
 }
 
-template <int SLOTS>
+template <int SLOTS, int ROWS>
 __global__ void __launch_bounds__(512)
 norm_quant_kernel(const uint4* h, const float* __restrict__ w, const float* __restrict__ rstd_in,
                   const unsigned int* amax_word, uint2* out, float* scale_out, int64_t rows, int nv) {
@@ -194,22 +194,36 @@ norm_quant_kernel(const uint4* h, const float* __restrict__ w, const float* __re
     const float s = scale_from_amax(__uint_as_float(*amax_word));
     const float inv = 1.f / s;
     if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) *scale_out = s;
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const float rstd = __ldg(rstd_in + row);
-        uint4 a[SLOTS];
+    // ROWS rows per CTA pass: this kernel moves only 1.5 bytes per element, so a CTA needs several rows'
+    // worth of loads in flight to be worth its launch.
+    for (int64_t row0 = (int64_t)blockIdx.x * ROWS; row0 < rows; row0 += (int64_t)gridDim.x * ROWS) {
+        uint4 a[ROWS][SLOTS];
+        float rstd[ROWS];
 #pragma unroll
-        for (int q = 0; q < SLOTS; ++q) {
-            const int v = q * blockDim.x + threadIdx.x;
-            if (v < nv) a[q] = ld_stream(h + row * nv + v);
+        for (int r = 0; r < ROWS; ++r) {
+            const int64_t row = row0 + r;
+            rstd[r] = row < rows ? __ldg(rstd_in + row) : 0.f;
+#pragma unroll
+            for (int q = 0; q < SLOTS; ++q) {
+                const int v = q * blockDim.x + threadIdx.x;
+                if (row < rows && v < nv) a[r][q] = ld_stream(h + row * nv + v);
+            }
         }
 #pragma unroll
         for (int q = 0; q < SLOTS; ++q) {
             const int v = q * blockDim.x + threadIdx.x;
             if (v < nv) {
-                float2 p[4];
-                unpack8x2(a[q], p);
-                const uint4 normed = scale8(p, rstd, ld_weight4(w + v * 8), ld_weight4(w + v * 8 + 4));   // bf16, as the norm kernel writes it
-                st_stream8(out + row * nv + v, quant8(normed, inv));
+                const float4 w0 = ld_weight4(w + v * 8), w1 = ld_weight4(w + v * 8 + 4);
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) {
+                    const int64_t row = row0 + r;
+                    if (row < rows) {
+                        float2 p[4];
+                        unpack8x2(a[r][q], p);
+                        const uint4 normed = scale8(p, rstd[r], w0, w1);      // bf16, as the norm kernel writes it
+                        st_stream8(out + row * nv + v, quant8(normed, inv));
+                    }
+                }
             }
         }
     }
@@ -237,6 +251,7 @@ static int launch_quant_flat(const void* x, void* out, float* scale_out, unsigne
     return finish_launch(2);
 }
 
+
 template <bool FUSE_ADD>
 static int launch_norm_quant(const void* x, const void* r, const float* w, void* out_res, void* out_fp8,
                              float* scale_out, void* workspace, int64_t rows, int64_t cols, float eps, cudaStream_t st) {
@@ -257,6 +272,7 @@ static int launch_norm_quant(const void* x, const void* r, const float* w, void*
     block = block > 512 ? 512 : (block + 31) / 32 * 32;
     const int slots = static_cast<int>((nv + block - 1) / block);
     const int grid = grid_for(rows, 1, 0x7fffffff);
+    const int qrows = tune("quant.rows_per_cta", 2);
     const float inv_cols = 1.0f / static_cast<float>(cols);
     auto X = static_cast<const uint4*>(x);
     auto R = static_cast<const uint4*>(r);
@@ -267,7 +283,11 @@ static int launch_norm_quant(const void* x, const void* r, const float* w, void*
     do {                                                                                                        \
         launch_kernel(norm_stats_kernel<S, FUSE_ADD>, grid, block, 0, st, X, R, w, OR, rstd, amax_word, rows,   \
                       (int)nv, inv_cols, eps);                                                                  \
-        launch_kernel(norm_quant_kernel<S>, grid, block, 0, st, H, w, static_cast<const float*>(rstd),          \
+        if (qrows >= 4) launch_kernel(norm_quant_kernel<S, 4>, grid_for(rows, 4, 0x7fffffff), block, 0, st, H, w, static_cast<const float*>(rstd), \
+                      static_cast<const unsigned int*>(amax_word), Q, scale_out, rows, (int)nv);                \
+        else if (qrows >= 2) launch_kernel(norm_quant_kernel<S, 2>, grid_for(rows, 2, 0x7fffffff), block, 0, st, H, w, static_cast<const float*>(rstd), \
+                      static_cast<const unsigned int*>(amax_word), Q, scale_out, rows, (int)nv);                \
+        else launch_kernel(norm_quant_kernel<S, 1>, grid_for(rows, 1, 0x7fffffff), block, 0, st, H, w, static_cast<const float*>(rstd), \
                       static_cast<const unsigned int*>(amax_word), Q, scale_out, rows, (int)nv);                \
     } while (0)
     if (slots <= 1) NMT_NQ_CASE(1);

@@ -30,6 +30,7 @@ static Knob g_knobs[] = {
     {"norm.rows_per_cta", {0}},   // CTA-per-row variant: rows a CTA loads together (1 or 2)
     {"norm.tma_rows", {0}},       // rows per TMA stage
     {"norm.tma_stages", {0}},
+    {"quant.rows_per_cta", {0}},  // rows a CTA of the norm -> e4m3 pass handles together (1, 2 or 4)
     // gated rmsnorm (bf16)
     {"gated.variant", {0}},       // 0 = auto, 1 = warp-per-group registers, 2 = TMA-staged rows
     {"gated.block", {0}},

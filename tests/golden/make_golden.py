@@ -82,7 +82,8 @@ def main() -> None:
     np.savez_compressed(os.path.join(HERE, "dump_mlp_block.npz"), **{k: mlp[k] for k in keep})
 
     mam = run_dump(a.reference, "dump_mamba_block.py", "mamba_block")
-    keep = ["input", "block_norm_w", "normed", "scan_y", "gate", "gnorm_w", "gnormed", "mixer_out", "expected", "meta"]
+    keep = ["input", "block_norm_w", "in_proj_w", "conv1d_w", "conv1d_b", "A_log", "D", "dt_bias", "gnorm_w", "out_proj_w",
+            "normed", "scan_y", "gate", "gnormed", "mixer_out", "expected", "meta"]
     np.savez_compressed(os.path.join(HERE, "dump_mamba_block.npz"), **{k: mam[k] for k in keep})
 
     ref = lift_functions(os.path.join(a.reference, "tools", "dump_mamba_block.py"), ["plain_rmsnorm", "gated_rmsnorm"])

@@ -78,3 +78,51 @@ def test_mlp_block_at_model_width_shim_equals_stock(built_lib):
     rel = ((outs[0] - outs[1]).norm() / outs[0].norm()).item()
     assert rel < 5e-3, rel
     assert (outs[0] - outs[1]).abs().max().item() < 0.15
+
+
+@pytest.fixture(scope="module")
+def mamba_golden():
+    d = golden("dump_mamba_block.npz")
+    f = lambda k: torch.from_numpy(d[k].copy()).cuda()  # noqa: E731
+    names = ["input", "block_norm_w", "in_proj_w", "conv1d_w", "conv1d_b", "A_log", "D", "dt_bias", "gnorm_w", "out_proj_w"]
+    g = {k: f(k) for k in names}
+    g["want"] = f("expected").reshape(24, 64)
+    return g
+
+
+def _run_mamba(lib, g, bf16):
+    bf = torch.bfloat16
+    cast = (lambda t: t.to(bf)) if bf16 else (lambda t: t)
+    x, in_proj, out_proj = cast(g["input"]), cast(g["in_proj_w"]), cast(g["out_proj_w"])
+    out = torch.empty(24, 64, dtype=x.dtype, device="cuda")
+    fn = lib.blk_mamba_forward_bf16 if bf16 else lib.blk_mamba_forward_fp32
+    rc = fn(_p(x), _p(g["block_norm_w"]), _p(in_proj), _p(g["conv1d_w"]), _p(g["conv1d_b"]), _p(g["A_log"]), _p(g["D"]),
+            _p(g["dt_bias"]), _p(g["gnorm_w"]), _p(out_proj), _p(out), 1, 24)
+    torch.cuda.synchronize()
+    lib.blk_free_allocator()
+    assert rc == 0
+    return out.float()
+
+
+def test_reference_mamba_block_on_the_drop_in_matches_its_golden(built_lib, mamba_golden):
+    """The reference's Mamba-2 block, unchanged, with its RMSNorm, gated RMSNorm and residual add served by this
+    library, reproduces the golden of tools/dump_mamba_block.py within the reference's own block-test
+    tolerances (tests/model/test_mamba_block.cu: fp32 1e-3, bf16 1.5e-1)."""
+    shim = _load("libref_mamba_shim.so")
+    before = built_lib.nmt_launch_count()
+    out32 = _run_mamba(shim, mamba_golden, bf16=False)
+    assert (out32 - mamba_golden["want"]).abs().max().item() < 1e-3
+    out16 = _run_mamba(shim, mamba_golden, bf16=True)
+    assert (out16 - mamba_golden["want"]).abs().max().item() < 1.5e-1
+    assert built_lib.nmt_launch_count() - before == 6        # norm, gated norm, add: once per precision
+
+
+def test_reference_mamba_block_on_its_own_kernels_is_reported(mamba_golden):
+    """Same block on the reference's own kernels.  Its gated RMSNorm reduces through a shared-memory word that all
+    32 lanes of a warp store to (ops/reduce.cuh:280-287); where that race resolves wrongly the block misses its
+    own golden.  Recorded, not asserted: the outcome belongs to the reference, not to this library."""
+    stock = _load("libref_mamba_stock.so")
+    for bf16, tol in ((False, 1e-3), (True, 1.5e-1)):
+        err = (_run_mamba(stock, mamba_golden, bf16) - mamba_golden["want"]).abs().max().item()
+        print(f"reference mamba block on its own kernels, {'bf16' if bf16 else 'fp32'}: max abs err {err:.3e} "
+              f"(reference tolerance {tol:g}) -> {'within' if err < tol else 'OUTSIDE'}")
