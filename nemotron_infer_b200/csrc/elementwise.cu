@@ -33,6 +33,7 @@ __global__ void __launch_bounds__(MAXB)
 ew_stream_kernel(const uint4* a, const uint4* b, uint4* out, int64_t nv) {
     pdl_wait();
     const int64_t tile_vecs = (int64_t)blockDim.x * U;
+#pragma unroll 1
     for (int64_t base = (int64_t)blockIdx.x * tile_vecs; base < nv; base += (int64_t)gridDim.x * tile_vecs) {
         uint4 va[U], vb[U];
 #pragma unroll
@@ -57,6 +58,7 @@ template <int OP>
 __global__ void __launch_bounds__(256)
 ew_f32_kernel(const float* a, const float* b, float* out, int64_t n) {
     pdl_wait();
+#pragma unroll 1
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         const float x = a[i];
         if (OP == kOpRelu2) out[i] = x > 0.f ? x * x : (x == x ? 0.f : x);

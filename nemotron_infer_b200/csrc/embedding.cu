@@ -17,6 +17,7 @@ embedding_rowwarp_kernel(const uint4* __restrict__ table, const IdT* __restrict_
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * warps_per_cta;
+#pragma unroll 1
     for (int64_t t = warp0; t < num_tokens; t += nwarps) {
         const int64_t id = static_cast<int64_t>(__ldg(ids + t));
         const bool ok = vocab <= 0 || (id >= 0 && id < vocab);
@@ -47,6 +48,7 @@ embedding_generic_kernel(const uint4* __restrict__ table, const IdT* __restrict_
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * warps_per_cta;
+#pragma unroll 1
     for (int64_t t = warp0; t < num_tokens; t += nwarps) {
         const int64_t id = static_cast<int64_t>(__ldg(ids + t));
         const bool ok = vocab <= 0 || (id >= 0 && id < vocab);

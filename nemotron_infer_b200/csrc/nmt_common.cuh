@@ -84,12 +84,13 @@ __device__ __forceinline__ uint4 add_bf16x8_rn(const uint4& a, const uint4& b) {
 }
 __device__ __forceinline__ uint32_t relu2_bf16x2(uint32_t u) {
     // fma.rn.relu.bf16x2 (x * 1 + 0, clamped at zero): one FMA-pipe instruction per pair; NaN stays NaN
-    // and -0 becomes +0.  The reference uses the same instruction (ops/elementwise.cuh:256-268).
-    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&u);
-    const __nv_bfloat162 one = __float2bfloat162_rn(1.f), zero = __float2bfloat162_rn(0.f);
-    x = __hfma2_relu(x, one, zero);
-    x = __hmul2(x, x);
-    return *reinterpret_cast<uint32_t*>(&x);
+    // and -0 becomes +0.  The reference uses the same instruction (ops/elementwise.cuh:256-268).  The two
+    // constants are written as bit patterns: built with a conversion intrinsic they were re-converted on
+    // every call and the conversion pipe, not memory, set the pace.
+    uint32_t r;
+    asm("fma.rn.relu.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(u), "r"(0x3F803F80u), "r"(0u));
+    asm("mul.bf16x2 %0, %1, %1;" : "=r"(r) : "r"(r));
+    return r;
 }
 // out = (p * rstd) * w for the eight elements of one vector, in that association order.
 __device__ __forceinline__ uint4 scale8(const float2 (&p)[4], float rstd, const float4& w0, const float4& w1) {

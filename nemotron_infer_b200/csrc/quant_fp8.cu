@@ -67,6 +67,7 @@ amax_kernel(const uint4* x, unsigned int* amax_word, int64_t nv) {
     pdl_wait();
     float m = 0.f;
     const int64_t tile = (int64_t)blockDim.x * U;
+#pragma unroll 1
     for (int64_t base = (int64_t)blockIdx.x * tile; base < nv; base += (int64_t)gridDim.x * tile) {
         uint4 v[U];
 #pragma unroll
@@ -97,6 +98,7 @@ quant_kernel(const uint4* x, uint2* out, const unsigned int* amax_word, float* s
     const float inv = 1.f / s;
     if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) *scale_out = s;
     const int64_t tile = (int64_t)blockDim.x * U;
+#pragma unroll 1
     for (int64_t base = (int64_t)blockIdx.x * tile; base < nv; base += (int64_t)gridDim.x * tile) {
         uint4 v[U];
 #pragma unroll
@@ -131,6 +133,7 @@ norm_stats_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, u
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     int flip = 0;
     float m = 0.f;
+#pragma unroll 1
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x, flip ^= 1) {
         uint4 a[SLOTS], b[SLOTS];
 #pragma unroll
@@ -196,6 +199,7 @@ norm_quant_kernel(const uint4* h, const float* __restrict__ w, const float* __re
     if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) *scale_out = s;
     // ROWS rows per CTA pass: this kernel moves only 1.5 bytes per element, so a CTA needs several rows'
     // worth of loads in flight to be worth its launch.
+#pragma unroll 1
     for (int64_t row0 = (int64_t)blockIdx.x * ROWS; row0 < rows; row0 += (int64_t)gridDim.x * ROWS) {
         uint4 a[ROWS][SLOTS];
         float rstd[ROWS];

@@ -22,6 +22,7 @@ rmsnorm_rowwarp_kernel(const uint4* x, const uint4* r,
     const int warps_per_cta = blockDim.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * warps_per_cta;
+#pragma unroll 1
 
     for (int64_t row = warp0; row < rows; row += nwarps) {
         const uint4* xr = x + row * nv;
@@ -93,6 +94,7 @@ rmsnorm_ctarow_kernel(const uint4* x, const uint4* r, const float* __restrict__ 
     __shared__ __align__(16) float s_part[2][ROWS][16];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     int flip = 0;
+#pragma unroll 1
     for (int64_t row0 = (int64_t)blockIdx.x * ROWS; row0 < rows; row0 += (int64_t)gridDim.x * ROWS, flip ^= 1) {
         uint4 a[ROWS][SLOTS], b[ROWS][SLOTS];
 #pragma unroll
@@ -165,6 +167,7 @@ rmsnorm_rowcta_kernel(const uint4* x, const uint4* r,
     __shared__ float s_part[8];
     __shared__ float s_total;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll 1
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint4* xr = x + row * nv;
         float ss = 0.f;
@@ -219,6 +222,7 @@ rmsnorm_f32_kernel(const float* __restrict__ x, float* y, const float* __restric
     __shared__ float s_part[8];
     __shared__ float s_total;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll 1
     for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const float* xr = x + row * cols;
         float ss = 0.f;

@@ -42,6 +42,7 @@ norm_tma_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, uin
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
+#pragma unroll 1
             for (int64_t tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++issued) {
                 const int s = issued % stages;
                 const uint32_t use = issued / stages;
@@ -66,6 +67,7 @@ norm_tma_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, uin
 
     const int c = warp - 1;
     int k = 0;
+#pragma unroll 1
     for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++k) {
         const int s = k % stages;
         if (!mbar_wait(full + s, (k / stages) & 1)) return;
