@@ -31,6 +31,7 @@ static Knob g_knobs[] = {
     {"norm.tma_rows", {0}},       // rows per TMA stage
     {"norm.tma_stages", {0}},
     {"quant.rows_per_cta", {0}},  // rows a CTA of the norm -> e4m3 pass handles together (1, 2 or 4)
+    {"quant.wide", {0}},          // norm -> e4m3 pass on 256-bit loads / 16-byte stores: 1 = yes, 2 = no (default)
     // gated rmsnorm (bf16)
     {"gated.variant", {0}},       // 0 = auto, 1 = warp-per-group registers, 2 = TMA-staged rows
     {"gated.block", {0}},

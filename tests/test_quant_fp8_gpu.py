@@ -104,6 +104,33 @@ def test_norm_quant_fused_equals_unfused_and_golden(ops, T, cols):
     assert float(s3.item()) == float(s4.item()) and torch.equal(bytes_of(q3), bytes_of(q4))
 
 
+@pytest.mark.parametrize("wide,qrows", [(2, 1), (2, 4), (1, 4), (1, 2)])
+def test_norm_quant_pass_layouts_agree(ops, wide, qrows):
+    """The e4m3 pass has a 16-byte-access and a 32-byte-access layout and 1/2/4 rows per CTA: same bytes from all,
+    including from a source that is only 16-byte aligned (which must fall back to the narrow layout)."""
+    try:
+        ops.tune("quant.wide", wide)
+        ops.tune("quant.rows_per_cta", qrows)
+        for T, cols in ((1027, 3136), (3, 16), (50, 4096), (9, 8200)):
+            x, r, w = og.cfg1_inputs(T, cols)
+            xd, rd, wd = x.cuda(), r.cuda(), w.cuda()
+            res, q, s = ops.rmsnorm_quant_fp8(xd, wd, r=rd)
+            _, normed = ops.add_rmsnorm(xd, rd, wd)
+            q2, s2 = ops.quantize_fp8(normed)
+            assert float(s.item()) == float(s2.item()) and torch.equal(bytes_of(q), bytes_of(q2)), (T, cols)
+            # 16-byte aligned but not 32-byte aligned x (plain norm + quant reads x in pass 2)
+            buf = torch.empty(T * cols + 8, dtype=BF, device="cuda")
+            xo = buf[8:].view(T, cols)
+            xo.copy_(xd)
+            assert xo.data_ptr() % 32 == 16
+            q3, s3 = ops.rmsnorm_quant_fp8(xo, wd)
+            q4, s4 = ops.quantize_fp8(ops.rmsnorm(xd, wd))
+            assert float(s3.item()) == float(s4.item()) and torch.equal(bytes_of(q3), bytes_of(q4)), (T, cols)
+    finally:
+        ops.tune("quant.wide", 0)
+        ops.tune("quant.rows_per_cta", 0)
+
+
 def test_norm_quant_in_place_residual_and_reused_workspace(ops):
     x, r, w = og.cfg1_inputs(513)
     ws = ops.fp8_workspace(513, "cuda")
