@@ -169,6 +169,14 @@ int nmt_add_rmsnorm_quant_fp8(const void* x, const void* r, const float* w, void
                               float* scale_out, void* workspace, int64_t rows, int64_t cols, float eps,
                               void* stream);
 
+/* Gated RMSNorm fused with the maximum its quantiser needs (the FP8 Mamba block quantises the gated norm's
+ * output right away, model/mamba_block.cuh:415-419): out_bf16 = rmsnorm_gated_bf16(y, z, w) as usual, and
+ * out_fp8 / *scale_out = quantize(out_bf16) without a separate maximum pass over out_bf16.
+ * `amax_scratch` is one device uint32, as in nmt_quantize_fp8. */
+int nmt_rmsnorm_gated_quant_fp8(const void* y, const void* z, const float* w, void* out_bf16, void* out_fp8,
+                                float* scale_out, unsigned int* amax_scratch, int64_t rows, int64_t cols,
+                                int64_t group_size, float eps, void* stream);
+
 /* nmt_add_rmsnorm_quant_fp8 for callers that cannot provide the workspace.  This entry point has no
  * counterpart in the reference.
  *

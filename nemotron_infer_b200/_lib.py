@@ -40,6 +40,7 @@ PROTOTYPES = {
     "nmt_fp8_workspace_bytes": (_i64, [_i64]),
     "nmt_rmsnorm_quant_fp8": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _f, _p]),
     "nmt_add_rmsnorm_quant_fp8": (_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _f, _p]),
+    "nmt_rmsnorm_gated_quant_fp8": (_int, [_p, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _f, _p]),
     "nmt_add_rmsnorm_quant_fp8_static": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f, _p]),
     "nmt_tune_set": (_int, [C.c_char_p, _int]),
     "nmt_tune_get": (_int, [C.c_char_p, C.POINTER(_int)]),

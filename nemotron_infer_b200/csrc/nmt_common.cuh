@@ -103,6 +103,19 @@ __device__ __forceinline__ uint4 scale8(const float2 (&p)[4], float rstd, const 
     return pack8x2(o);
 }
 
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Non-negative floats order like their bit patterns, so the running maximum is an unsigned atomicMax
+// (ops/gemm.cuh:254-255).  Most callers lose the race to an earlier, larger value: peek first.
+__device__ __forceinline__ void publish_max(unsigned int* word, float v) {
+    const unsigned int bits = __float_as_uint(v);
+    if (bits > *reinterpret_cast<volatile unsigned int*>(word)) atomicMax(word, bits);
+}
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
 // Butterfly sum: every lane ends with the warp total.
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

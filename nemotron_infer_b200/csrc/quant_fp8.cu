@@ -43,19 +43,6 @@ __device__ __forceinline__ uint2 quant8(const uint4& v, float inv) {
 __device__ __forceinline__ void st_stream8(uint2* p, const uint2& v) {
     asm volatile("st.global.L1::no_allocate.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-// Non-negative floats order like their bit patterns, so the running maximum is an unsigned atomicMax
-// (ops/gemm.cuh:254-255).  Most callers lose the race to an earlier, larger value: peek first.
-__device__ __forceinline__ void publish_max(unsigned int* word, float v) {
-    const unsigned int bits = __float_as_uint(v);
-    if (bits > *reinterpret_cast<volatile unsigned int*>(word)) atomicMax(word, bits);
-}
-__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
-
 enum { kXfIdentity = 0, kXfRelu2 = 1 };
 
 // ---------------------------------------------------------------------------------------------
@@ -416,9 +403,34 @@ static void* static_scratch_address(int* status) {
     return p;
 }
 
+int launch_gated_bf16(const void* y, const void* z, const float* w, void* out, int64_t rows, int64_t cols,
+                      int64_t group_size, float eps, unsigned int* amax_word, bool* tracked, cudaStream_t st);   // rmsnorm_gated.cu
+
 }  // namespace nmt
 
 extern "C" {
+
+int nmt_rmsnorm_gated_quant_fp8(const void* y, const void* z, const float* w, void* out_bf16, void* out_fp8,
+                                float* scale_out, unsigned int* amax_scratch, int64_t rows, int64_t cols,
+                                int64_t group_size, float eps, void* stream) {
+    using namespace nmt;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows < 0 || cols <= 0 || (cols % 8) != 0) return NMT_ERR_SHAPE;
+    if (rows == 0) return NMT_OK;
+    if (!out_fp8 || !amax_scratch) return NMT_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(out_fp8) & 7u) || !aligned4(amax_scratch) || (scale_out && !aligned4(scale_out))) return NMT_ERR_ALIGN;
+    if (cudaMemsetAsync(amax_scratch, 0, sizeof(unsigned int), st) != cudaSuccess) return finish_launch(0);
+    bool tracked = false;
+    int s = launch_gated_bf16(y, z, w, out_bf16, rows, cols, group_size, eps, amax_scratch, &tracked, st);
+    if (s != NMT_OK) return s;
+    const int64_t nv = rows * cols / 8;
+    constexpr int U = 4, B = 256;
+    if (!tracked)     // group shape outside the register kernel: take the maximum in a pass of its own
+        launch_kernel(amax_kernel<kXfIdentity, U>, ew_grid(nv, B, U), B, 0, st, static_cast<const uint4*>(out_bf16), amax_scratch, nv);
+    launch_kernel(quant_kernel<kXfIdentity, U>, ew_grid(nv, B, U), B, 0, st, static_cast<const uint4*>(out_bf16),
+                  static_cast<uint2*>(out_fp8), static_cast<const unsigned int*>(amax_scratch), scale_out, nv);
+    return finish_launch(tracked ? 1 : 2);
+}
 
 int nmt_add_rmsnorm_quant_fp8_static(const void* x, const void* r, const float* w, void* out_res, void* out_fp8,
                                      float* scale_out, int64_t rows, int64_t cols, float eps, void* stream) {

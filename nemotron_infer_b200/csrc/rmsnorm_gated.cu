@@ -34,10 +34,14 @@ __device__ __forceinline__ float2 silu2_sfu(const float2& z) {
 }
 __device__ __forceinline__ float silu_exact(float z) { return z / (1.0f + expf(-z)); }
 
-template <int SLOTS, int RPI>
+// TRACK: also keep the largest |output| (for the e4m3 quantiser that follows in the FP8 Mamba block,
+// model/mamba_block.cuh:415-419), so that quantiser needs no maximum pass of its own.
+template <int SLOTS, int RPI, bool TRACK = false>
 __global__ void __launch_bounds__(256)
 gated_groupwarp_kernel(const uint4* y, const uint4* z, const float* __restrict__ w, uint4* out,
-                       int64_t items, int groups, int group_mask, int gv, float inv_gs, float eps) {
+                       int64_t items, int groups, int group_mask, int gv, float inv_gs, float eps,
+                       unsigned int* amax_word = nullptr) {
+    float amax = 0.f;
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int warps_per_cta = blockDim.x >> 5;
@@ -90,10 +94,22 @@ gated_groupwarp_kernel(const uint4* y, const uint4* z, const float* __restrict__
 #pragma unroll
             for (int s = 0; s < SLOTS; ++s) {
                 const int v = s * 32 + lane;
-                if (v < gv)
-                    st_stream(out + it * gv + v, scale8(g[s], rstd, ld_weight4(wg + v * 8), ld_weight4(wg + v * 8 + 4)));
+                if (v < gv) {
+                    const uint4 o = scale8(g[s], rstd, ld_weight4(wg + v * 8), ld_weight4(wg + v * 8 + 4));
+                    st_stream(out + it * gv + v, o);
+                    if (TRACK) {
+                        float f[8];
+                        unpack8(o, f);
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(f[k]));
+                    }
+                }
             }
         }
+    }
+    if (TRACK) {
+        amax = warp_max(amax);
+        if (lane == 0 && amax > 0.f) publish_max(amax_word, amax);
     }
     pdl_trigger();
 }
@@ -145,18 +161,13 @@ static int check_gated(const void* y, const void* z, const float* w, const void*
     return NMT_OK;
 }
 
-}  // namespace nmt
-
-extern "C" {
-
-int nmt_rmsnorm_gated_bf16(const void* y, const void* z, const float* w, void* out,
-                           int64_t rows, int64_t cols, int64_t group_size, float eps, void* stream) {
-    using namespace nmt;
+int launch_gated_bf16(const void* y, const void* z, const float* w, void* out, int64_t rows, int64_t cols,
+                      int64_t group_size, float eps, unsigned int* amax_word, bool* tracked, cudaStream_t st) {
+    if (tracked) *tracked = false;
     int s = check_gated(y, z, w, out, rows, cols, group_size);
     if (s != NMT_OK || rows == 0) return s;
     if ((cols % 8) != 0) return NMT_ERR_SHAPE;
     if (!aligned16(y) || !aligned16(z) || !aligned16(out) || !aligned16(w)) return NMT_ERR_ALIGN;
-    cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int64_t groups = cols / group_size;
     const int64_t items = rows * groups;
 
@@ -181,8 +192,9 @@ int nmt_rmsnorm_gated_bf16(const void* y, const void* z, const float* w, void* o
     auto O = static_cast<uint4*>(out);
 #define NMT_GATED_CASE(S)                                                                              \
     do {                                                                                               \
-        if (rpi >= 2) launch_kernel(gated_groupwarp_kernel<S, 2>, grid, block, 0, st, Y, Z, w, O, items, (int)groups, gmask, gv, inv_gs, eps); \
-        else launch_kernel(gated_groupwarp_kernel<S, 1>, grid, block, 0, st, Y, Z, w, O, items, (int)groups, gmask, gv, inv_gs, eps);   \
+        if (amax_word) { launch_kernel(gated_groupwarp_kernel<S, 1, true>, grid_for(items, wpc, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff), block, 0, st, Y, Z, w, O, items, (int)groups, gmask, gv, inv_gs, eps, amax_word); if (tracked) *tracked = true; } \
+        else if (rpi >= 2) launch_kernel(gated_groupwarp_kernel<S, 2>, grid, block, 0, st, Y, Z, w, O, items, (int)groups, gmask, gv, inv_gs, eps, (unsigned int*)nullptr); \
+        else launch_kernel(gated_groupwarp_kernel<S, 1>, grid, block, 0, st, Y, Z, w, O, items, (int)groups, gmask, gv, inv_gs, eps, (unsigned int*)nullptr);   \
     } while (0)
     if (slots <= 1) NMT_GATED_CASE(1);
     else if (slots <= 2) NMT_GATED_CASE(2);
@@ -192,6 +204,16 @@ int nmt_rmsnorm_gated_bf16(const void* y, const void* z, const float* w, void* o
     else NMT_GATED_CASE(8);
 #undef NMT_GATED_CASE
     return finish_launch(1);
+}
+
+}  // namespace nmt
+
+extern "C" {
+
+int nmt_rmsnorm_gated_bf16(const void* y, const void* z, const float* w, void* out,
+                           int64_t rows, int64_t cols, int64_t group_size, float eps, void* stream) {
+    return nmt::launch_gated_bf16(y, z, w, out, rows, cols, group_size, eps, nullptr, nullptr,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 int nmt_rmsnorm_gated_f32(const float* y, const float* z, const float* w, float* out,

@@ -39,6 +39,7 @@ SHAPES = {
     "quantize_fp8": (8192, 3136 * (2 + 2 + 1)),                  # amax pass + quantising pass over [T, 3136]
     "add_rmsnorm_quant_fp8": (8192, 3136 * (2 + 2 + 2 + 2 + 1)),  # x, r -> out_res ; out_res -> e4m3
     "relu2_quant_fp8": (8192, 12544 * (2 + 2 + 1)),              # u twice in, e4m3 out
+    "gated_quant_fp8": (16384, 6144 * (2 + 2 + 2 + 2 + 1)),      # y, z -> bf16 out (+max) ; bf16 out -> e4m3
 }
 
 
@@ -79,6 +80,12 @@ def make_case(op: str, T: int, dev):
         u = (2 * rn(T, 12544)).to(BF)
         q = torch.empty(T, 12544, dtype=torch.float8_e4m3fn, device=dev)
         return lambda: ops.quantize_fp8(u, out=q, relu2_first=True)
+    if op == "gated_quant_fp8":
+        y, z = rn(T, 6144).to(BF), rn(T, 6144).to(BF)
+        w = 1 + 0.1 * rn(6144)
+        o = torch.empty_like(y)
+        q = torch.empty(T, 6144, dtype=torch.float8_e4m3fn, device=dev)
+        return lambda: ops.rmsnorm_gated_quant_fp8(y, z, w, 768, out_bf16=o, out=q)
     if op == "add_rmsnorm_quant_fp8":
         x, r = rn(T, 3136).to(BF), rn(T, 3136).to(BF)
         w = 1 + 0.1 * rn(3136)

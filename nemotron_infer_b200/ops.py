@@ -205,6 +205,23 @@ def rmsnorm_quant_fp8(x: torch.Tensor, w: torch.Tensor, r: torch.Tensor | None =
     return out_res, out, scale
 
 
+def rmsnorm_gated_quant_fp8(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, group_size: int, eps: float = EPS,
+                            out_bf16: torch.Tensor | None = None, out: torch.Tensor | None = None):
+    """(out_bf16, q, scale): gated RMSNorm whose kernel also tracks max|out|, followed by the e4m3 quantiser."""
+    out_bf16 = torch.empty_like(y) if out_bf16 is None else out_bf16
+    out = _fp8_out(y, out)
+    _dev(y, z, w, out_bf16, out)
+    if y.dtype != torch.bfloat16 or z.dtype != y.dtype or out_bf16.dtype != y.dtype or w.dtype != torch.float32:
+        raise ValueError("y, z, out_bf16 must be bf16 and w fp32")
+    rows, cols = _rows_cols(y)
+    scale = torch.empty(1, dtype=torch.float32, device=y.device)
+    amax = torch.empty(1, dtype=torch.int32, device=y.device)
+    _lib.check(_lib.load().nmt_rmsnorm_gated_quant_fp8(y.data_ptr(), z.data_ptr(), w.data_ptr(), out_bf16.data_ptr(),
+                                                       out.data_ptr(), scale.data_ptr(), amax.data_ptr(), rows, cols,
+                                                       int(group_size), eps, _stream()), "rmsnorm_gated_quant_fp8")
+    return out_bf16, out, scale
+
+
 def tune(key: str, value: int) -> None:
     """Sets a launch-shape / variant knob (see nmt_tune_set in include/nemotron_b200.h)."""
     _lib.check(_lib.load().nmt_tune_set(key.encode(), int(value)), f"tune({key})")

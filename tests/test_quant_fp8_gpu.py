@@ -131,6 +131,20 @@ def test_norm_quant_pass_layouts_agree(ops, wide, qrows):
         ops.tune("quant.rows_per_cta", 0)
 
 
+@pytest.mark.parametrize("T,cols,gs", [(4096, 6144, 768), (300, 7680, 960), (7, 192, 64), (5, 120, 12), (3, 8192, 4096)])
+def test_gated_norm_quant_equals_gated_then_quant(ops, T, cols, gs):
+    y, z, w = og.cfg2_inputs(T, cols)
+    yd, zd, wd = y.cuda(), z.cuda(), w.cuda()
+    out, q, s = ops.rmsnorm_gated_quant_fp8(yd, zd, wd, gs)
+    out2 = ops.rmsnorm_gated(yd, zd, wd, gs)
+    q2, s2 = ops.quantize_fp8(out2)
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+    assert float(s.item()) == float(s2.item()) and torch.equal(bytes_of(q), bytes_of(q2))
+    want_q, want_s = og.quantize_fp8(og.gated_rmsnorm_bf16(y, z, w, gs))
+    assert abs(float(s.item()) - float(want_s)) <= float(want_s) * 2.0 ** -7
+    assert int((og.e4m3_ordered(q.cpu()) - og.e4m3_ordered(want_q)).abs().max()) <= 1
+
+
 def test_norm_quant_in_place_residual_and_reused_workspace(ops):
     x, r, w = og.cfg1_inputs(513)
     ws = ops.fp8_workspace(513, "cuda")
