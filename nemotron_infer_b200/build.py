@@ -85,12 +85,32 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+def build_pybind(force: bool = False) -> str:
+    """Compiles nemotron_infer_b200/pybind/binding.cpp into an importable module next to it, linked to the library."""
+    import sysconfig
+    import pybind11
+    build()
+    src = os.path.join(PKG_DIR, "pybind", "binding.cpp")
+    out = os.path.join(PKG_DIR, "pybind", "binding" + sysconfig.get_config_var("EXT_SUFFIX"))
+    if force or _stale(out, [src, LIB_PATH, os.path.join(INCLUDE, "nemotron_b200.h")]):
+        cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden",
+               "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"], "-I", INCLUDE,
+               src, "-o", out, "-L", PKG_DIR, "-lnemotron_b200", "-Wl,-rpath,$ORIGIN/.."]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"pybind module failed to build:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register/spill reports")
+    ap.add_argument("--pybind", action="store_true", help="also build the pybind11 module nemotron_infer_b200.pybind.binding")
     a = ap.parse_args()
     print(build(force=a.force, verbose=a.verbose))
+    if a.pybind:
+        print(build_pybind(force=a.force))
 
 
 if __name__ == "__main__":

@@ -35,6 +35,7 @@ def built_lib():
     """Builds (if stale) and loads the C-ABI library; fails loudly when it cannot."""
     from nemotron_infer_b200 import _lib, build
     build.build()
+    build.build_pybind()
     return _lib.load()
 
 

@@ -111,3 +111,18 @@ def test_binding_raises_on_rejected_arguments(built_lib):
         B.rmsnorm(0, BUF, BUF, 4)
     assert e.value.status == 1
     B.rmsnorm(BUF, BUF, BUF, 0)      # M == 0 is a no-op, like a zero-size grid in the reference
+
+
+def test_pybind_module_has_the_reference_surface(built_lib):
+    """The compiled pybind11 module keeps the reference's names, arity and None return for the hot ops
+    (binding.cu:59-73, 214-232) and raises instead of invoking undefined behaviour."""
+    from nemotron_infer_b200.pybind import binding as B
+    assert (B.HIDDEN, B.INTER, B.VOCAB, B.CONV_DIM, B.IN_PROJ, B.G) == (3136, 12544, 131072, 9728, 17504, 8)
+    assert B.embedding(BUF, BUF, BUF, 0) is None          # (table, ids, out, num_tokens)
+    assert B.rmsnorm(BUF, BUF, BUF, 0) is None             # (in, out, w, M)
+    assert B.reset_allocator() is None and B.free_allocator() is None
+    assert B.add_rmsnorm(BUF, BUF + 64, BUF, BUF, BUF + 128, 0) is None
+    with pytest.raises(RuntimeError, match="null pointer"):
+        B.rmsnorm(0, BUF, BUF, 4)
+    with pytest.raises(TypeError):
+        B.rmsnorm(BUF, BUF, BUF)                            # same arity as the reference

@@ -415,6 +415,45 @@ def test_cta_per_row_norm_variant(ops, block):
         ops.tune("norm.block", 0)
 
 
+def test_pybind_module_and_ctypes_mirror_on_device(ops):
+    """The two Python-level drop-ins for the reference's `binding` module (compiled pybind11 and ctypes), driven
+    the way engine.py drives the reference: tensors by data_ptr(), sizes as ints (engine.py:40-42, 248, 261)."""
+    from nemotron_infer_b200 import binding as C
+    from nemotron_infer_b200.pybind import binding as P
+    T = 130
+    table, ids = og.cfg4_inputs(T, vocab=P.VOCAB // 64)      # a slice of the vocabulary is enough
+    x, r, w = og.cfg1_inputs(T)
+    want_emb = og.embedding(ids, table)
+    want_res, want_norm = og.add_rmsnorm_bf16(x, r, w)
+    td, idd, xd, rd, wd = table.cuda(), ids.long().cuda(), x.cuda(), r.cuda(), w.cuda()
+    for B in (P, C):
+        B.set_device(torch.cuda.current_device())
+        out = torch.empty(T, B.HIDDEN, dtype=BF, device="cuda")
+        B.embedding(td.data_ptr(), idd.data_ptr(), out.data_ptr(), T)
+        B.sync()
+        assert torch.equal(out.cpu().view(torch.int16), want_emb.view(torch.int16))
+        B.rmsnorm(xd.data_ptr(), out.data_ptr(), wd.data_ptr(), T)
+        B.sync()
+        assert_ulp(out, og.rmsnorm_bf16(x, w), "binding.rmsnorm")
+        res = torch.empty_like(xd)
+        B.add_rmsnorm(xd.data_ptr(), rd.data_ptr(), wd.data_ptr(), res.data_ptr(), out.data_ptr(), T)
+        B.sync()
+        assert torch.equal(res.cpu(), want_res)
+        assert_ulp(out, want_norm, "binding.add_rmsnorm")
+        y, z, gw = og.cfg2_inputs(9, B.H * B.P)
+        go = torch.empty(9, B.H * B.P, dtype=BF, device="cuda")
+        yd, zd, gwd = y.cuda(), z.cuda(), gw.cuda()            # keep the device tensors alive across the call
+        B.rmsnorm_gated(yd.data_ptr(), zd.data_ptr(), gwd.data_ptr(), go.data_ptr(), 9)
+        B.sync()
+        assert_ulp(go, og.gated_rmsnorm_bf16(y, z, gw, 960), "binding.rmsnorm_gated")
+        u = og.cfg3_inputs(5)
+        ao = torch.empty(5, B.INTER, dtype=BF, device="cuda")
+        ud = u.cuda()
+        B.relu2(ud.data_ptr(), ao.data_ptr(), 5)
+        B.sync()
+        assert torch.equal(ao.cpu(), og.relu2_bf16(u))
+
+
 # ---------------------------------------------------------------------------------------------
 # the reference's own kernels, recompiled for sm_100a, as a second checker
 # ---------------------------------------------------------------------------------------------
