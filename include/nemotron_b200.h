@@ -139,6 +139,23 @@ int nmt_embedding_bf16_i32(const void* table, const int32_t* ids, void* out,
                            int64_t num_tokens, int64_t hidden, int64_t vocab,
                            int32_t* err_flag, void* stream);
 
+/* ---- Mamba-2 causal conv1d + SiLU (with the x | B | C split) -------------------- */
+
+/* y[b, t, c] = silu(bias[c] + sum_k w[c, k] * xbc[b, t - 3 + k, c]), k = 0..3, zero before t = 0; bf16 in/out,
+ * fp32 taps, bias and accumulation.  Replaces nemotron::ops::mamba2::causal_conv1d_prefill_bf16
+ * (ops/mamba2/causal_conv1d.cuh:369-389) TOGETHER WITH the three strided copies that split its output
+ * (model/mamba_block.cuh:199-207): channels [0, n0) are written to out0 as a contiguous [batch*S, n0] tensor,
+ * [n0, n0+n1) to out1, the rest to out2.  Pass n1 = n2 = 0 (out1 = out2 = NULL) for the unsplit
+ * [batch*S, conv_dim] output of the reference.  n0, n1, n2 multiples of 8.  state_out (may be NULL) receives the
+ * last three raw inputs per channel, [batch, conv_dim, 3] fp32, the layout the decode step continues from. */
+int nmt_causal_conv1d_silu_split_bf16(const void* xbc, const float* w, const float* bias, void* out0, void* out1,
+                                      void* out2, int64_t n0, int64_t n1, int64_t n2, float* state_out,
+                                      int64_t S, int64_t batch, void* stream);
+
+/* fp32 twin, unsplit; replaces causal_conv1d_prefill_fp32 (ops/mamba2/causal_conv1d.cuh:115-127). */
+int nmt_causal_conv1d_silu_f32(const float* x, const float* w, const float* bias, float* y, float* state_out,
+                               int64_t conv_dim, int64_t S, int64_t batch, void* stream);
+
 /* ---- Per-tensor FP8 (e4m3) activation quantisation ---------------------------- */
 
 /* out_fp8 = e4m3(clamp(x / s, +-448)), s = max|x| / 448 (1/448 for an all-zero tensor), *scale_out = s.

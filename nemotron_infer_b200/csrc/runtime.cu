@@ -32,6 +32,9 @@ static Knob g_knobs[] = {
     {"norm.tma_stages", {0}},
     {"quant.rows_per_cta", {0}},  // rows a CTA of the norm -> e4m3 pass handles together (1, 2 or 4)
     {"quant.wide", {0}},          // norm -> e4m3 pass on 256-bit loads / 16-byte stores: 1 = yes, 2 = no (default)
+    {"conv.chunk", {0}},          // causal conv1d: time steps per thread (4, 8, 16, 32 or 64)
+    {"conv.pairs", {0}},          // causal conv1d: channel pairs per thread (2 = 8-byte vectors, 4 = 16-byte vectors)
+    {"conv.unroll", {0}},         // causal conv1d: loads issued ahead of use (4 or 8)
     // gated rmsnorm (bf16)
     {"gated.variant", {0}},       // 0 = auto, 1 = warp-per-group registers, 2 = TMA-staged rows
     {"gated.block", {0}},

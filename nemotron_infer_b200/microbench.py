@@ -35,6 +35,7 @@ SHAPES = {
     "relu2": (8192, 2 * 12544 * 2),
     "add": (8192, 3 * 3136 * 2),
     "embedding": (65536, 2 * 3136 * 2 + 4),
+    "conv1d_split": (16384, 9728 * (2 + 2)),                     # xBC in, x | B | C out (Mamba-2 conv1d + SiLU)
     # e4m3 activation quantisation (the step after the norm / activation in the FP8 blocks)
     "quantize_fp8": (8192, 3136 * (2 + 2 + 1)),                  # amax pass + quantising pass over [T, 3136]
     "add_rmsnorm_quant_fp8": (8192, 3136 * (2 + 2 + 2 + 2 + 1)),  # x, r -> out_res ; out_res -> e4m3
@@ -72,6 +73,10 @@ def make_case(op: str, T: int, dev):
         u = (2 * rn(T, 12544)).to(BF)
         o = torch.empty_like(u)
         return lambda: ops.relu2(u, out=o)
+    if op == "conv1d_split":
+        xbc = rn(1, T, 9728).to(BF)
+        w, b = 0.2 * rn(9728, 4), 0.1 * rn(9728)
+        return lambda: ops.causal_conv1d_silu(xbc, w, b, split=(7680, 1024, 1024))
     if op == "quantize_fp8":
         x = rn(T, 3136).to(BF)
         q = torch.empty(T, 3136, dtype=torch.float8_e4m3fn, device=dev)

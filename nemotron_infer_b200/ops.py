@@ -151,6 +151,42 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None =
     return out
 
 
+def causal_conv1d_silu(xbc: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, split: tuple[int, ...] | None = None,
+                       return_state: bool = False):
+    """Depthwise causal conv1d (4 taps) + bias + SiLU over xbc [batch, S, conv_dim] (bf16 or fp32), w [conv_dim, 4],
+    bias [conv_dim] fp32.  With split=(n0, n1, n2) the bf16 result comes back as three contiguous tensors
+    (the x | B | C inputs of the scan) instead of one; return_state adds the [batch, conv_dim, 3] fp32 tail."""
+    if xbc.dim() != 3:
+        raise ValueError("xbc must be [batch, S, conv_dim]")
+    batch, S, C = xbc.shape
+    _dev(xbc, w, bias)
+    if w.dtype != torch.float32 or bias.dtype != torch.float32 or w.numel() != C * 4 or bias.numel() != C:
+        raise ValueError("w must be fp32 [conv_dim, 4] and bias fp32 [conv_dim]")
+    state = torch.empty(batch, C, 3, dtype=torch.float32, device=xbc.device) if return_state else None
+    sp = state.data_ptr() if state is not None else None
+    lib = _lib.load()
+    if xbc.dtype == torch.float32:
+        if split is not None:
+            raise ValueError("the split form is bf16 only")
+        y = torch.empty_like(xbc)
+        _lib.check(lib.nmt_causal_conv1d_silu_f32(xbc.data_ptr(), w.data_ptr(), bias.data_ptr(), y.data_ptr(), sp, C, S, batch,
+                                                  _stream()), "causal_conv1d_silu")
+        outs = (y,)
+    elif xbc.dtype == torch.bfloat16:
+        sizes = tuple(split) if split is not None else (C,)
+        if sum(sizes) != C or len(sizes) > 3:
+            raise ValueError("split must be up to three sizes that add up to conv_dim")
+        outs = tuple(torch.empty(batch, S, n, dtype=xbc.dtype, device=xbc.device) for n in sizes)
+        ptrs = [o.data_ptr() for o in outs] + [None] * (3 - len(outs))
+        ns = list(sizes) + [0] * (3 - len(sizes))
+        _lib.check(lib.nmt_causal_conv1d_silu_split_bf16(xbc.data_ptr(), w.data_ptr(), bias.data_ptr(), ptrs[0], ptrs[1], ptrs[2],
+                                                         ns[0], ns[1], ns[2], sp, S, batch, _stream()), "causal_conv1d_silu")
+    else:
+        raise ValueError("xbc must be bf16 or fp32")
+    res = outs if split is not None else outs[0]
+    return (res, state) if return_state else res
+
+
 def _fp8_out(like: torch.Tensor, out: torch.Tensor | None) -> torch.Tensor:
     out = torch.empty(like.shape, dtype=torch.float8_e4m3fn, device=like.device) if out is None else out
     if out.dtype != torch.float8_e4m3fn or out.shape != like.shape:

@@ -11,6 +11,7 @@
 #include "ops/reduce.cuh"        // rmsnorm_{fp32,bf16}, rmsnorm_gated_{fp32,bf16}<Group>
 #include "ops/elementwise.cuh"   // elementwise_ops_{fp32,bf16}<Op>
 #include "ops/embedding.cuh"     // embedding_lookup<Hidden>
+#include "ops/mamba2/causal_conv1d.cuh"   // causal_conv1d_prefill_{fp32,bf16}
 
 using namespace nemotron::ops;
 using bf16 = __nv_bfloat16;
@@ -94,6 +95,13 @@ REF_API int ref_embedding_i64(const void* table, const int64_t* ids, void* out, 
         case 3136: embedding_lookup<3136>(T, ids, O, num_tokens, st); break;
         default: return -1;
     }
+    return last();
+}
+
+REF_API int ref_causal_conv1d_bf16(const void* x, const float* w, const float* b, void* y, float* state_out, int conv_dim,
+                                   int S, int batch, void* st) {
+    mamba2::causal_conv1d_prefill_bf16<64>(static_cast<const bf16*>(x), w, b, static_cast<bf16*>(y), state_out, conv_dim, S,
+                                           batch, static_cast<cudaStream_t>(st));
     return last();
 }
 

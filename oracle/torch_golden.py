@@ -84,6 +84,29 @@ def relu2_bf16(u: torch.Tensor) -> torch.Tensor:
     return relu2(u).to(torch.bfloat16)
 
 
+# --- Mamba-2 depthwise causal conv1d + SiLU (tools/dump_mamba_block.py:126-130; tools/ref_full_model.py mamba()) ---
+
+def causal_conv1d_silu(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """x [batch, S, C]; w [C, K] (the emitter's [C, 1, K] flattened); b [C]."""
+    S, C, K = x.shape[1], x.shape[2], w.shape[1]
+    h = x.float().transpose(1, 2)
+    h = F.conv1d(h, w.reshape(C, 1, K), bias=b, padding=K - 1, groups=C)[..., :S]
+    return F.silu(h.transpose(1, 2))
+
+
+def causal_conv1d_silu_bf16(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    assert x.dtype == torch.bfloat16
+    return causal_conv1d_silu(x, w, b).to(torch.bfloat16)
+
+
+def conv_state_tail(x: torch.Tensor, K: int = 4) -> torch.Tensor:
+    """[batch, C, K-1] fp32: the last K-1 raw inputs per channel, zero-padded on the left when S < K-1
+    (what causal_conv1d_prefill leaves for the decode step, ops/mamba2/causal_conv1d.cuh:86-92)."""
+    batch, S, C = x.shape
+    pad = F.pad(x.float().transpose(1, 2), (K - 1, 0))
+    return pad[..., pad.shape[-1] - (K - 1):].contiguous()
+
+
 # --- per-tensor e4m3 quantisation of a bf16 activation tensor -----------------------
 # Restates fp8_amax_kernel + fp8_quant_kernel (ops/gemm.cuh:257-289): amax = max|x| over the bf16 tensor,
 # s = amax / 448 (1/448 when s < 1e-10), q = e4m3(clamp(x * (1/s), -448, 448)), all in fp32.

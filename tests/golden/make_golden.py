@@ -12,7 +12,8 @@ Two sources, neither of which copies reference text into this repository:
    raw float32 dumps we keep the stage tensors that pin the hot-path ops:
      mlp:   input, block_norm_w -> normed (RMSNorm);  up -> act (relu^2);
             input + down -> expected (residual add); up_proj_w / down_proj_w for the whole-block check
-     mamba: input, block_norm_w -> normed;  scan_y, gate, gnorm_w -> gnormed (gated RMSNorm)
+     mamba: input, block_norm_w -> normed;  scan_y, gate, gnorm_w -> gnormed (gated RMSNorm);
+            xbc, conv1d_w, conv1d_b -> xbc_conv (causal conv1d + SiLU)
 2. The functions `plain_rmsnorm` and `gated_rmsnorm` are lifted out of
    tools/dump_mamba_block.py with `ast` at run time and evaluated on the seeded
    inputs of the benchmark configurations (small row counts, full widths), with
@@ -83,7 +84,7 @@ def main() -> None:
 
     mam = run_dump(a.reference, "dump_mamba_block.py", "mamba_block")
     keep = ["input", "block_norm_w", "in_proj_w", "conv1d_w", "conv1d_b", "A_log", "D", "dt_bias", "gnorm_w", "out_proj_w",
-            "normed", "scan_y", "gate", "gnormed", "mixer_out", "expected", "meta"]
+            "normed", "xbc", "xbc_conv", "scan_y", "gate", "gnormed", "mixer_out", "expected", "meta"]
     np.savez_compressed(os.path.join(HERE, "dump_mamba_block.npz"), **{k: mam[k] for k in keep})
 
     ref = lift_functions(os.path.join(a.reference, "tools", "dump_mamba_block.py"), ["plain_rmsnorm", "gated_rmsnorm"])

@@ -35,6 +35,15 @@ def test_norms_match_mamba_dump_stages():
     torch.testing.assert_close(got.reshape(-1), _t(d["gnormed"]), rtol=1e-5, atol=1e-6)
 
 
+def test_conv1d_matches_mamba_dump_stage():
+    d = golden("dump_mamba_block.npz")
+    x = _t(d["xbc"]).reshape(1, 24, 128)
+    got = og.causal_conv1d_silu(x, _t(d["conv1d_w"]).reshape(128, 4), _t(d["conv1d_b"]))
+    torch.testing.assert_close(got.reshape(-1), _t(d["xbc_conv"]), rtol=1e-6, atol=1e-6)
+    tail = og.conv_state_tail(x)
+    assert torch.equal(tail[0, :, 2], x[0, 23]) and torch.equal(tail[0, :, 0], x[0, 21])
+
+
 def test_cfg0_fp32_rmsnorm_fixture():
     d = golden("cfg0_fp32.npz")
     x, w = og.cfg0_inputs()
