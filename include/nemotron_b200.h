@@ -156,6 +156,14 @@ int nmt_causal_conv1d_silu_split_bf16(const void* xbc, const float* w, const flo
 int nmt_causal_conv1d_silu_f32(const float* x, const float* w, const float* bias, float* y, float* state_out,
                                int64_t conv_dim, int64_t S, int64_t batch, void* stream);
 
+/* ---- W8A16 GEMV (single-token decode projections) --------------------------------- */
+
+/* y[n] = bf16((sum_k e4m3(W[n,k]) * bf16(x[k])) * w_scale[n]), fp32 accumulation.  Replaces
+ * nemotron::ops::gemv_fp8 (ops/gemv.cuh:87-104; kernel :48-85), same arguments: W is [N, K] row-major e4m3 with
+ * one fp32 scale per output row, x is K bf16 activations (not quantised).  K % 16 == 0, W 16-byte aligned. */
+int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale, void* y_bf16, int64_t N, int64_t K,
+                   void* stream);
+
 /* ---- Per-tensor FP8 (e4m3) activation quantisation ---------------------------- */
 
 /* out_fp8 = e4m3(clamp(x / s, +-448)), s = max|x| / 448 (1/448 for an all-zero tensor), *scale_out = s.

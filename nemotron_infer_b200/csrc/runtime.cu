@@ -35,6 +35,9 @@ static Knob g_knobs[] = {
     {"conv.chunk", {0}},          // causal conv1d: time steps per thread (4, 8, 16, 32 or 64)
     {"conv.pairs", {0}},          // causal conv1d: channel pairs per thread (2 = 8-byte vectors, 4 = 16-byte vectors)
     {"conv.unroll", {0}},         // causal conv1d: loads issued ahead of use (4 or 8)
+    {"gemv.split", {0}},          // W8A16 GEMV: K-slices per row (1, 2, 4, 8); 0 = by K
+    {"gemv.variant", {0}},        // W8A16 GEMV: 1 = whole-unit loads with prefetch (default), 2 = looped loads
+    {"gemv.ctas_per_sm", {0}},    // W8A16 GEMV: persistent CTAs per SM; 0 = by shared-memory footprint
     // gated rmsnorm (bf16)
     {"gated.variant", {0}},       // 0 = auto, 1 = warp-per-group registers, 2 = TMA-staged rows
     {"gated.block", {0}},

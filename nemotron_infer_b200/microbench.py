@@ -36,6 +36,9 @@ SHAPES = {
     "add": (8192, 3 * 3136 * 2),
     "embedding": (65536, 2 * 3136 * 2 + 4),
     "conv1d_split": (16384, 9728 * (2 + 2)),                     # xBC in, x | B | C out (Mamba-2 conv1d + SiLU)
+    # single-token decode projections (weight streaming): "tokens" is the number of output rows N here
+    "gemv_up": (12544, 3136),        # up_proj   N = 12544, K = 3136: 3136 weight bytes per output row
+    "gemv_down": (3136, 12544),      # down_proj N = 3136,  K = 12544
     # e4m3 activation quantisation (the step after the norm / activation in the FP8 blocks)
     "quantize_fp8": (8192, 3136 * (2 + 2 + 1)),                  # amax pass + quantising pass over [T, 3136]
     "add_rmsnorm_quant_fp8": (8192, 3136 * (2 + 2 + 2 + 2 + 1)),  # x, r -> out_res ; out_res -> e4m3
@@ -73,6 +76,13 @@ def make_case(op: str, T: int, dev):
         u = (2 * rn(T, 12544)).to(BF)
         o = torch.empty_like(u)
         return lambda: ops.relu2(u, out=o)
+    if op in ("gemv_up", "gemv_down"):
+        K = SHAPES[op][1]
+        W = (rn(T, K) * 20).clamp(-448, 448).to(torch.float8_e4m3fn)
+        x = rn(K).to(BF)
+        sc = torch.rand(T, device=dev) * 0.01
+        y = torch.empty(T, dtype=BF, device=dev)
+        return lambda: ops.gemv_w8a16(x, W, sc, out=y)
     if op == "conv1d_split":
         xbc = rn(1, T, 9728).to(BF)
         w, b = 0.2 * rn(9728, 4), 0.1 * rn(9728)
@@ -107,7 +117,7 @@ def make_case(op: str, T: int, dev):
     raise ValueError(op)
 
 
-def run_op(op: str, T: int, reps: int, warmup: int, dev, batch: int = 10) -> dict:
+def run_op(op: str, T: int, reps: int, warmup: int, dev, batch: int = 10, graph: bool = False) -> dict:
     _, bpt = SHAPES[op]
     nbytes = bpt * T
     nsets = max(2, min(8, -(-2 * L2_BYTES // max(nbytes, 1)) + 1))
@@ -116,19 +126,33 @@ def run_op(op: str, T: int, reps: int, warmup: int, dev, batch: int = 10) -> dic
         fns[i % nsets]()
     torch.cuda.synchronize()
     evs = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
-    evs[0].record()
-    n = 0
-    for i in range(reps):
-        for _ in range(batch):
-            fns[n % nsets]()
-            n += 1
-        evs[i + 1].record()
+    if graph:
+        # Kernels of a few microseconds are bound by the host's launch rate when driven from Python; a CUDA graph
+        # of one batch (rotating over the buffer sets) shows the device-side rate a captured decode loop gets.
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for k in range(batch):
+                fns[k % nsets]()
+        g.replay()
+        torch.cuda.synchronize()
+        evs[0].record()
+        for i in range(reps):
+            g.replay()
+            evs[i + 1].record()
+    else:
+        evs[0].record()
+        n = 0
+        for i in range(reps):
+            for _ in range(batch):
+                fns[n % nsets]()
+                n += 1
+            evs[i + 1].record()
     torch.cuda.synchronize()
     us = sorted(evs[i].elapsed_time(evs[i + 1]) * 1e3 / batch for i in range(reps))
     med, mn = statistics.median(us), us[0]
     peak = measured_peak()
     gbs = nbytes / med / 1e3
-    return {"op": op, "tokens": T, "bytes_per_token": bpt, "buffer_sets": nsets, "reps": reps, "batch": batch,
+    return {"op": op, "tokens": T, "bytes_per_token": bpt, "buffer_sets": nsets, "reps": reps, "batch": batch, "graph": graph,
             "median_us": round(med, 2), "min_us": round(mn, 2), "gbs": round(gbs, 1),
             "gbs_best": round(nbytes / mn / 1e3, 1), "tokens_per_s": round(T / med * 1e6, 0),
             "frac_of_nominal_8000": round(gbs / NOMINAL_GBS, 4),
@@ -165,6 +189,7 @@ def main() -> None:
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=10, help="back-to-back launches per timed interval")
+    ap.add_argument("--graph", action="store_true", help="capture each batch in a CUDA graph (default for the gemv ops)")
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--tune", action="append", default=[], metavar="key=value")
     a = ap.parse_args()
@@ -179,7 +204,7 @@ def main() -> None:
             print(json.dumps(run_chain(a.tokens or 64, a.reps, f"cuda:{a.device}")), flush=True)
             continue
         T = a.tokens or SHAPES[op][0]
-        print(json.dumps(run_op(op, T, a.reps, a.warmup, f"cuda:{a.device}", a.batch)), flush=True)
+        print(json.dumps(run_op(op, T, a.reps, a.warmup, f"cuda:{a.device}", a.batch, a.graph or op.startswith("gemv"))), flush=True)
         torch.cuda.empty_cache()
 
 

@@ -187,6 +187,20 @@ def causal_conv1d_silu(xbc: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, s
     return (res, state) if return_state else res
 
 
+def gemv_w8a16(x: torch.Tensor, W: torch.Tensor, w_scale: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[N] = (W[N, K] (e4m3) @ x[K] (bf16)) * w_scale[N], fp32 accumulation, bf16 result: the decode projection."""
+    N, K = W.shape
+    out = torch.empty(N, dtype=torch.bfloat16, device=x.device) if out is None else out
+    _dev(x, W, w_scale, out)
+    if W.dtype != torch.float8_e4m3fn or x.dtype != torch.bfloat16 or w_scale.dtype != torch.float32 or out.dtype != torch.bfloat16:
+        raise ValueError("W must be float8_e4m3fn, x and out bf16, w_scale fp32")
+    if x.numel() != K or w_scale.numel() != N or out.numel() != N:
+        raise ValueError("shape mismatch")
+    _lib.check(_lib.load().nmt_gemv_w8a16(x.data_ptr(), W.data_ptr(), w_scale.data_ptr(), out.data_ptr(), N, K, _stream()),
+               "gemv_w8a16")
+    return out
+
+
 def _fp8_out(like: torch.Tensor, out: torch.Tensor | None) -> torch.Tensor:
     out = torch.empty(like.shape, dtype=torch.float8_e4m3fn, device=like.device) if out is None else out
     if out.dtype != torch.float8_e4m3fn or out.shape != like.shape:

@@ -11,6 +11,7 @@
 #include "ops/reduce.cuh"        // rmsnorm_{fp32,bf16}, rmsnorm_gated_{fp32,bf16}<Group>
 #include "ops/elementwise.cuh"   // elementwise_ops_{fp32,bf16}<Op>
 #include "ops/embedding.cuh"     // embedding_lookup<Hidden>
+#include "ops/gemv.cuh"                   // gemv_fp8
 #include "ops/mamba2/causal_conv1d.cuh"   // causal_conv1d_prefill_{fp32,bf16}
 
 using namespace nemotron::ops;
@@ -102,6 +103,12 @@ REF_API int ref_causal_conv1d_bf16(const void* x, const float* w, const float* b
                                    int S, int batch, void* st) {
     mamba2::causal_conv1d_prefill_bf16<64>(static_cast<const bf16*>(x), w, b, static_cast<bf16*>(y), state_out, conv_dim, S,
                                            batch, static_cast<cudaStream_t>(st));
+    return last();
+}
+
+REF_API int ref_gemv_fp8(const void* x, const void* W, const float* w_scale, void* y, int N, int K, void* st) {
+    gemv_fp8(static_cast<const bf16*>(x), static_cast<const __nv_fp8_e4m3*>(W), w_scale, static_cast<bf16*>(y), N, K,
+             static_cast<cudaStream_t>(st));
     return last();
 }
 

@@ -107,6 +107,24 @@ def conv_state_tail(x: torch.Tensor, K: int = 4) -> torch.Tensor:
     return pad[..., pad.shape[-1] - (K - 1):].contiguous()
 
 
+# --- W8A16 GEMV (tests/ops/test_gemm.cu:505-531: gemv_fp8_ref and quant_weight_perrow) -------------------------
+
+def quant_weight_perrow(Wf: torch.Tensor):
+    """Per-output-row e4m3 quantisation of an fp32 weight matrix: (W_e4m3, w_scale)."""
+    amax = Wf.abs().amax(dim=1)
+    scale = amax / 448.0
+    scale = torch.where(scale < 1e-10, torch.full_like(scale, 1.0 / 448.0), scale)
+    q = torch.clamp(Wf * (1.0 / scale)[:, None], -448.0, 448.0).to(torch.float8_e4m3fn)
+    return q, scale.float()
+
+
+def gemv_w8a16(x: torch.Tensor, W: torch.Tensor, w_scale: torch.Tensor) -> torch.Tensor:
+    """y[n] = (sum_k float(W[n,k]) * float(x[k])) * w_scale[n], as fp32 (round to bf16 for the kernel's output).
+    Accumulated in float64 here so that the checker itself adds no summation-order noise."""
+    assert W.dtype == torch.float8_e4m3fn and x.dtype == torch.bfloat16
+    return ((W.float().double() @ x.float().double()) * w_scale.double()).float()
+
+
 # --- per-tensor e4m3 quantisation of a bf16 activation tensor -----------------------
 # Restates fp8_amax_kernel + fp8_quant_kernel (ops/gemm.cuh:257-289): amax = max|x| over the bf16 tensor,
 # s = amax / 448 (1/448 when s < 1e-10), q = e4m3(clamp(x * (1/s), -448, 448)), all in fp32.

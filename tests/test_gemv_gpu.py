@@ -1,0 +1,100 @@
+"""W8A16 GEMV (single-token decode projection) against the reference test's CPU formulation
+(tests/ops/test_gemm.cu:505-513), its input recipe and tolerance (:539-589), and the reference's own kernel."""
+import ctypes
+
+import pytest
+import torch
+
+from oracle import torch_golden as og
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def ops(built_lib):
+    from nemotron_infer_b200 import ops as _ops
+    built_lib.nmt_set_device(torch.cuda.current_device())
+    return _ops
+
+
+def check(got, want):
+    """The reference test's bar (max(0.02, 2 %)) and, tighter, the bf16 rounding of the exact sum: fp32 partial
+    sums in a different order may move the result by an ulp only when the sum nearly cancels."""
+    got, want = got.float().cpu(), want.float()
+    tol = torch.maximum(torch.full_like(want, 0.02), 0.02 * want.abs())
+    assert bool(((got - want).abs() <= tol).all())
+    rep = og.ulp_report(got.to(BF), want.to(BF))
+    assert rep["mismatch_frac"] <= 0.05 and rep["max_ulp"] <= 4, rep
+
+
+def test_reference_test_recipe(ops):
+    N, K = 64, 3136                                  # tests/ops/test_gemm.cu:541-546
+    x = ((torch.arange(K) * 13 % 17).float() * 0.1 - 0.8).to(BF)
+    Wf = ((torch.arange(N * K) * 7 % 23).float() * 0.05 - 0.55).reshape(N, K)
+    W, sc = og.quant_weight_perrow(Wf)
+    check(ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()), og.gemv_w8a16(x, W, sc))
+
+
+@pytest.mark.parametrize("N,K", [(12544, 3136), (3136, 12544), (3136, 7680), (17504, 3136), (1, 16), (7, 48), (33, 8192),
+                                 (5, 20000), (131, 4096 + 16)])
+def test_model_and_odd_shapes(ops, N, K):
+    g = torch.Generator().manual_seed(N + K)
+    x = torch.randn(K, generator=g).to(BF)
+    W, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
+    check(ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()), og.gemv_w8a16(x, W, sc))
+
+
+def test_every_e4m3_value_and_split_variants(ops):
+    # one row per e4m3 bit pattern (NaN patterns excluded) against a one-hot x: the conversion must be exact
+    codes = torch.tensor([c for c in range(256) if (c & 0x7F) != 0x7F], dtype=torch.uint8)
+    K = 16
+    W = torch.zeros(codes.numel(), K, dtype=torch.uint8)
+    W[:, 5] = codes
+    W = W.view(torch.float8_e4m3fn)
+    x = torch.zeros(K, dtype=BF)
+    x[5] = 1.0
+    sc = torch.ones(codes.numel())
+    got = ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()).cpu().float()
+    assert torch.equal(got, W.float()[:, 5])
+    g = torch.Generator().manual_seed(3)
+    xk = torch.randn(6272, generator=g).to(BF)
+    Wk, sk = og.quant_weight_perrow(0.05 * torch.randn(100, 6272, generator=g))
+    want = og.gemv_w8a16(xk, Wk, sk)
+    try:
+        for variant, split, per_sm in ((1, 2, 1), (1, 4, 2), (1, 8, 3), (2, 1, 1), (2, 2, 2), (2, 4, 1), (2, 8, 3)):
+            ops.tune("gemv.variant", variant)        # 1 = whole-unit loads, 2 = looped loads
+            ops.tune("gemv.split", split)
+            ops.tune("gemv.ctas_per_sm", per_sm)
+            check(ops.gemv_w8a16(xk.cuda(), Wk.cuda(), sk.cuda()), want)
+    finally:
+        for k in ("gemv.variant", "gemv.split", "gemv.ctas_per_sm"):
+            ops.tune(k, 0)
+
+
+def test_against_reference_kernel(ops, ref_kernels):
+    if ref_kernels is None or not hasattr(ref_kernels, "ref_gemv_fp8"):
+        pytest.skip("reference gemv kernel not built")
+    g = torch.Generator().manual_seed(9)
+    N, K = 12544, 3136
+    x = torch.randn(K, generator=g).to(BF).cuda()
+    W, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
+    Wd, sd = W.cuda(), sc.cuda()
+    ref = torch.empty(N, dtype=BF, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    ref_kernels.ref_set_device(torch.cuda.current_device())
+    assert ref_kernels.ref_gemv_fp8(p(x), p(Wd), p(sd), p(ref), N, K, None) == 0
+    torch.cuda.synchronize()
+    got = ops.gemv_w8a16(x, Wd, sd)
+    rep = og.ulp_report(got, ref)
+    assert rep["max_ulp"] <= 4 and rep["mismatch_frac"] <= 0.05, rep
+
+
+def test_gemv_argument_checks(built_lib):
+    L = built_lib
+    B = 0x7F0000000000
+    assert L.nmt_gemv_w8a16(B, B, B, B, 0, 3136, None) == 0
+    assert L.nmt_gemv_w8a16(B, B, B, B, 4, 3130, None) == 3
+    assert L.nmt_gemv_w8a16(B, None, B, B, 4, 3136, None) == 1
+    assert L.nmt_gemv_w8a16(B, B + 8, B, B, 4, 3136, None) == 2
+    assert L.nmt_gemv_w8a16(B, B, B, B, 4, 64000, None) == 5
