@@ -160,7 +160,9 @@ int nmt_causal_conv1d_silu_f32(const float* x, const float* w, const float* bias
 
 /* y[n] = bf16((sum_k e4m3(W[n,k]) * bf16(x[k])) * w_scale[n]), fp32 accumulation.  Replaces
  * nemotron::ops::gemv_fp8 (ops/gemv.cuh:87-104; kernel :48-85), same arguments: W is [N, K] row-major e4m3 with
- * one fp32 scale per output row, x is K bf16 activations (not quantised).  K % 16 == 0, W 16-byte aligned. */
+ * one fp32 scale per output row, x is K bf16 activations (not quantised).  K % 16 == 0, W 16-byte aligned.
+ * When K % 64 == 0 the products run on tensor cores with x held as f16 times a power of two taken from max|x|:
+ * exact for elements within 2^-28 of the maximum (nmt_tune_set("gemv.variant", 1) keeps fp32 products). */
 int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale, void* y_bf16, int64_t N, int64_t K,
                    void* stream);
 

@@ -195,10 +195,274 @@ gemv_w8a16_kernel(const __nv_bfloat16* __restrict__ x, const uint4* __restrict__
     pdl_trigger();
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core inner product.  The CUDA-core kernels above spend ~2.8 instructions per weight byte (convert,
+// convert, multiply-add) and are bound by instruction issue at ~3 TB/s.  mma.sync.m16n8k16 (f16 in, fp32
+// accumulate) does the multiply-adds and the f16 -> fp32 widening in one instruction per 256 weights per warp,
+// leaving one e4m3x2 -> f16x2 convert per two weights.
+//
+// A dot product does not care in which order k is visited as long as W and x agree, so a lane feeds the MMA
+// straight from the 16 contiguous weight bytes it loaded (no shuffles): in chunk c (64 values of k), lane
+// (g = lane / 4, t = lane % 4) holds bytes [t*16, t*16+16) of A-rows g and g+8, and MMA m of the chunk uses bytes
+// 4m..4m+3 of them; the x fragment is read with the same permutation.
+//
+// The 16 A-rows of a warp tile are R matrix rows x S "k-streams" (R * S = 16): stream s of a row is multiplied
+// with column s of B, which holds x for that stream's k range, so C[s*R + r][s] is a partial sum of matrix row r.
+// Together with SPLIT warps per tile this cuts every row into S * SPLIT slices of ~6 chunks, which gives short,
+// wide matrices (down_proj: 3136 x 12544) as many work units as tall ones.  All partial sums of a row meet in
+// shared memory and are added in a fixed order after one block barrier.
+//
+// x is staged as f16 scaled by a power of two chosen from max|x| (bf16 has 8 significant bits, f16 has 11, so
+// the conversion is exact for every element within 2^-28 of the maximum); the scale is undone on the fp32 sum.
+// ---------------------------------------------------------------------------------------------
+constexpr int kMmaGroup = 4;          // chunks (64 k each) per load group; two groups are in flight per warp
+constexpr int kMmaMaxChunks = 16;     // upper bound on chunks per work unit (keeps the slice count meaningful)
+
+// Bytes 0-1 / bytes 2-3 of a word of four e4m3 weights as an f16x2 register.
+__device__ __forceinline__ uint32_t e4m3_lo(uint32_t w) {
+    uint32_t h;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, lo; }" : "=r"(h) : "r"(w));
+    return h;
+}
+__device__ __forceinline__ uint32_t e4m3_hi(uint32_t w) {
+    uint32_t h;
+    asm("{ .reg .b16 lo, hi; mov.b32 {lo, hi}, %1; cvt.rn.f16x2.e4m3x2 %0, hi; }" : "=r"(h) : "r"(w));
+    return h;
+}
+// 16-byte streaming load that is skipped (v keeps its value) when on is false.
+__device__ __forceinline__ void ld_stream_if(uint4& v, const void* p, bool on) {
+    asm volatile("{ .reg .pred q; setp.ne.s32 q, %5, 0; @q ld.global.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4]; }"
+                 : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w) : "l"(p), "r"(static_cast<int>(on)) : "memory");
+}
+// Shared memory for x as f16 (K is a multiple of 64) followed by one chunk of zeros.
+__host__ __device__ constexpr size_t mma_x_bytes(int K) { return (size_t)K * 2 + 128; }
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int SPLIT, int S>           // S k-streams per tile, R = 16 / S matrix rows per tile
+__global__ void __launch_bounds__(kGemvWarps * 32)
+gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, const float* __restrict__ w_scale,
+                      __nv_bfloat16* __restrict__ y, int N, int K, int iters, int early_trigger) {
+    constexpr int R = 16 / S;
+    constexpr int TILES_PER_CTA = kGemvWarps / SPLIT;
+    constexpr int Q = S * SPLIT;                                   // k-slices per matrix row
+    constexpr int G = kMmaGroup;                                   // chunks per load group
+    extern __shared__ __align__(16) uint8_t smem_b[];
+    __half* xh = reinterpret_cast<__half*>(smem_b);                // K halves
+    float* part = reinterpret_cast<float*>(smem_b + mma_x_bytes(K));                   // [iters][warp][16]
+    __shared__ float s_red[kGemvWarps];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
+
+    // ---- this warp's slice geometry ----
+    const int kc = K / 64;                                         // chunks per row
+    // Slice q gets base chunks, the LAST rem slices one more: a short slice that reads one chunk past its end (to
+    // keep the loop uniform) then reads the first chunk of the next slice of the same row, which is inside the matrix.
+    const int base = kc / Q, rem = kc % Q;
+    auto slice_start = [&](int q) { return q * base + max(0, q - (Q - rem)); };
+    auto slice_len = [&](int q) { return base + (q >= Q - rem ? 1 : 0); };
+    const int split_id = warp % SPLIT, tile_in_cta = warp / SPLIT;
+    // A-rows of this lane: a = g and a = g + 8; stream = a / R, local row = a % R
+    const int sA = g / R, rA = g % R, sB = (g + 8) / R, rB = (g + 8) % R;
+    const int cA0 = slice_start(split_id * S + sA), cB0 = slice_start(split_id * S + sB);
+    // x fragment: lanes with g < S feed column g of B with stream g's k range
+    const int cX0 = g < S ? slice_start(split_id * S + g) : 0, nX = g < S ? slice_len(split_id * S + g) : 0;
+    const int nmax = base + (rem ? 1 : 0);
+    const int groups = (nmax + G - 1) / G;                         // load groups per work unit
+    const int total = iters * groups;                              // load groups of this warp, in order
+    const int ntiles = (N + R - 1) / R;
+
+    // Ragged edges are handled on the x side so that no weight register ever needs a zero fill: a row past N is read
+    // from row N-1 (its sum is never stored), a chunk past the end of a short stream is the next stream's first
+    // chunk (inside the matrix) and is multiplied with zeros, because lanes that have no x to contribute for a
+    // chunk (g >= S, or past their stream's end) read the zero block that follows x in shared memory.
+    const __half* xzero = xh + K;                                  // 64 halves of zero
+    const __half* xbase = xh + (size_t)cX0 * 64 + t * 16;
+    const size_t offA = (size_t)cA0 * 64 + t * 16, offB = (size_t)cB0 * 64 + t * 16;
+
+    // Load group (it, grp) = chunks [grp*G, grp*G + G) of work unit it, for both A-rows of this lane.
+    auto load_group = [&](uint4 (&wa)[G], uint4 (&wb)[G], int it, int grp) {
+        // Predicated loads, not branches: a branch around loads makes the compiler wait for them at the join.
+        const int tile = (it * gridDim.x + blockIdx.x) * TILES_PER_CTA + tile_in_cta;
+        const bool live = it < iters && tile < ntiles;             // warp-uniform
+        const int j0 = grp * G;
+        const int tl = min(tile, ntiles - 1);
+        const uint8_t* pa = W + (size_t)min(tl * R + rA, N - 1) * K + offA + j0 * 64;
+        const uint8_t* pb = W + (size_t)min(tl * R + rB, N - 1) * K + offB + j0 * 64;
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            const bool on = live && j0 + j < nmax;
+            ld_stream_if(wa[j], pa + j * 64, on);
+            ld_stream_if(wb[j], pb + j * 64, on);
+        }
+    };
+    float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};    // two chains, so an MMA does not wait for the one before it
+    auto compute_group = [&](const uint4 (&wa)[G], const uint4 (&wb)[G], int it, int grp) {
+        const int tile = (it * gridDim.x + blockIdx.x) * TILES_PER_CTA + tile_in_cta;
+        if (it >= iters) return;                                   // warp-uniform
+        if (tile < ntiles) {
+            const int j0 = grp * G;
+            if (grp == 0) c[0] = c[1] = c[2] = c[3] = d[0] = d[1] = d[2] = d[3] = 0.f;
+#pragma unroll
+            for (int j = 0; j < G; ++j) {
+                if (j0 + j < nmax) {                               // warp-uniform
+                    const uint4* xp = reinterpret_cast<const uint4*>(j0 + j < nX ? xbase + (j0 + j) * 64 : xzero);
+                    const uint4 x0 = xp[0], x1 = xp[1];
+                    const uint32_t wa_[4] = {wa[j].x, wa[j].y, wa[j].z, wa[j].w};
+                    const uint32_t wb_[4] = {wb[j].x, wb[j].y, wb[j].z, wb[j].w};
+                    const uint32_t xb_[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                    for (int mm = 0; mm < 4; ++mm)
+                        mma_f16((mm & 1) ? d : c, e4m3_lo(wa_[mm]), e4m3_lo(wb_[mm]), e4m3_hi(wa_[mm]), e4m3_hi(wb_[mm]), xb_[2 * mm], xb_[2 * mm + 1]);
+                }
+            }
+        }
+        if (grp == groups - 1) {
+            // C[a][n] is wanted for n = stream(a) only: lane (g, t) holds columns 2t, 2t+1 of A-rows g and g+8
+            float* pw = part + ((size_t)it * kGemvWarps + warp) * 16;
+            if (sA / 2 == t) pw[g] = c[sA & 1] + d[sA & 1];
+            if (sB / 2 == t) pw[g + 8] = c[2 + (sB & 1)] + d[2 + (sB & 1)];
+        }
+    };
+
+    // The weights are constants of the model, not an output of the preceding kernel: their first loads go out
+    // before the wait on that kernel, and before x is staged, so the stream is already running when x is ready.
+    uint4 wa0[G] = {}, wb0[G] = {}, wa1[G] = {}, wb1[G] = {};
+    load_group(wa0, wb0, 0, 0);
+    pdl_wait();
+
+    // ---- stage x: max|x| -> power-of-two scale -> f16 ----
+    // x is read once and kept in registers between the two steps when it fits (K <= 16384); every load is issued
+    // before the first use, so staging costs one trip to L2 plus two barriers.
+    constexpr int XW = 32;                                         // words (bf16 pairs) per thread held in registers
+    const uint32_t* xw = reinterpret_cast<const uint32_t*>(x);
+    const int words = K / 2;
+    const bool held = words <= XW * kGemvWarps * 32;               // block-uniform
+    uint32_t xr[XW];
+    float m = 0.f;
+    if (held) {
+#pragma unroll
+        for (int i = 0; i < XW; ++i) {
+            const int idx = threadIdx.x + i * kGemvWarps * 32;
+            xr[i] = idx < words ? __ldg(xw + idx) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < XW; ++i) m = fmaxf(m, fmaxf(fabsf(bf16_lo(xr[i])), fabsf(bf16_hi(xr[i]))));
+    } else {
+        for (int i = threadIdx.x; i < words; i += blockDim.x) {
+            const uint32_t u = xw[i];
+            m = fmaxf(m, fmaxf(fabsf(bf16_lo(u)), fabsf(bf16_hi(u))));
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    float mm = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGemvWarps; ++i) mm = fmaxf(mm, s_red[i]);
+    int e = 0;
+    if (mm > 0.f && mm < 3.0e38f) e = static_cast<int>((__float_as_uint(mm) >> 23) & 0xff) - 127 - 14;   // max|x| lands in [2^14, 2^15)
+    e = max(e, -100);                                              // keeps 2^-e and 2^e normal fp32 numbers
+    const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);      // 2^-e
+    if (held) {
+#pragma unroll
+        for (int i = 0; i < XW; ++i) {
+            const int idx = threadIdx.x + i * kGemvWarps * 32;
+            if (idx < words) reinterpret_cast<__half2*>(xh)[idx] = __floats2half2_rn(bf16_lo(xr[i]) * down, bf16_hi(xr[i]) * down);
+        }
+    } else {
+        for (int i = threadIdx.x; i < words; i += blockDim.x) {
+            const uint32_t u = xw[i];
+            reinterpret_cast<__half2*>(xh)[i] = __floats2half2_rn(bf16_lo(u) * down, bf16_hi(u) * down);
+        }
+    }
+    if (threadIdx.x < 32) reinterpret_cast<uint32_t*>(xh + K)[threadIdx.x] = 0u;
+    __syncthreads();
+
+    // ---- stream: the next group's loads are in flight while this group is multiplied ----
+    int cit = 0, cgrp = 0, lit = 0, lgrp = 0;                      // (work unit, group) being computed / loaded
+    auto step = [&](int& it, int& grp) { if (++grp == groups) { grp = 0; ++it; } };
+    step(lit, lgrp);
+#pragma unroll 1
+    while (cit < iters) {
+        load_group(wa1, wb1, lit, lgrp);
+        step(lit, lgrp);
+        compute_group(wa0, wb0, cit, cgrp);
+        step(cit, cgrp);
+        load_group(wa0, wb0, lit, lgrp);
+        step(lit, lgrp);
+        if (early_trigger && lit >= iters) pdl_trigger();          // every load of this warp has been issued
+        compute_group(wa1, wb1, cit, cgrp);
+        step(cit, cgrp);
+    }
+    __syncthreads();
+    // ---- combine: matrix row r of tile T = sum over streams s and split warps of part[..][s*R + r] ----
+    const float up = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);         // 2^e
+    for (int o = threadIdx.x; o < iters * TILES_PER_CTA * R; o += blockDim.x) {
+        const int it = o / (TILES_PER_CTA * R), rest = o % (TILES_PER_CTA * R);
+        const int tc = rest / R, r = rest % R;
+        const int row = ((it * gridDim.x + blockIdx.x) * TILES_PER_CTA + tc) * R + r;
+        if (row < N) {
+            float sum = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < SPLIT; ++sp)
+#pragma unroll
+                for (int s2 = 0; s2 < S; ++s2) sum += part[((size_t)it * kGemvWarps + tc * SPLIT + sp) * 16 + s2 * R + r];
+            y[row] = __float2bfloat16_rn((sum * up) * __ldg(w_scale + row));
+        }
+    }
+    if (!early_trigger) pdl_trigger();
+}
+
+template <int SPLIT, int S>
+static int launch_gemv_mma(const void* x, const void* W, const float* w_scale, void* y, int N, int K, cudaStream_t st) {
+    constexpr int R = 16 / S, TILES_PER_CTA = kGemvWarps / SPLIT;
+    auto kern = gemv_w8a16_mma_kernel<SPLIT, S>;
+    const int ntiles = (N + R - 1) / R;
+    const int ctas_needed = (ntiles + TILES_PER_CTA - 1) / TILES_PER_CTA;
+    const int per_sm = tune("gemv.ctas_per_sm", 2);
+    int iters = (ctas_needed + kSmCount * per_sm - 1) / (kSmCount * per_sm);      // passes per CTA ...
+    if (iters < 1) iters = 1;
+    const int grid = (ctas_needed + iters - 1) / iters;                           // ... evenly spread over the grid
+    const size_t smem = mma_x_bytes(K) + (size_t)iters * kGemvWarps * 16 * sizeof(float);
+    if (smem > 200 * 1024) return NMT_ERR_UNSUPPORTED;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return finish_launch(0);
+        configured[dev] = true;
+    }
+    launch_kernel(kern, grid, kGemvWarps * 32, smem, st, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(W),
+                  w_scale, static_cast<__nv_bfloat16*>(y), N, K, iters, tune("gemv.early_trigger", 1) == 1);
+    return finish_launch(1);
+}
+
+// Picks S * SPLIT so that a work unit is about six chunks; returns NMT_ERR_UNSUPPORTED when the shape does not fit.
+static int launch_gemv_mma_auto(const void* x, const void* W, const float* w_scale, void* y, int N, int K, cudaStream_t st) {
+    if ((K % 64) != 0) return NMT_ERR_UNSUPPORTED;
+    const int kc = K / 64;
+    int q = 1;
+    while (q < 64 && (kc + q - 1) / q > tune("gemv.unit_chunks", 7)) q *= 2;                                 // slices per row
+    if ((kc + q - 1) / q > kMmaMaxChunks) return NMT_ERR_UNSUPPORTED;
+    const int forced = tune("gemv.streams", 0);
+    int split = q >= 8 ? 8 : q, streams = q / split;
+    if (forced > 0 && forced <= 8 && q % forced == 0 && q / forced <= 8) { streams = forced; split = q / forced; }
+#define NMT_MMA_CASE(SP, ST) if (split == SP && streams == ST) return launch_gemv_mma<SP, ST>(x, W, w_scale, y, N, K, st)
+    NMT_MMA_CASE(1, 1); NMT_MMA_CASE(2, 1); NMT_MMA_CASE(4, 1); NMT_MMA_CASE(8, 1);
+    NMT_MMA_CASE(1, 2); NMT_MMA_CASE(2, 2); NMT_MMA_CASE(4, 2); NMT_MMA_CASE(8, 2);
+    NMT_MMA_CASE(1, 4); NMT_MMA_CASE(2, 4); NMT_MMA_CASE(4, 4); NMT_MMA_CASE(8, 4);
+    NMT_MMA_CASE(1, 8); NMT_MMA_CASE(2, 8); NMT_MMA_CASE(4, 8); NMT_MMA_CASE(8, 8);
+#undef NMT_MMA_CASE
+    return NMT_ERR_UNSUPPORTED;
+}
+
 template <int SPLIT>
 static int launch_gemv(const void* x, const void* W, const float* w_scale, void* y, int N, int kv, cudaStream_t st) {
     constexpr int UNROLL = 4;
-    const bool unit = (kv + SPLIT - 1) / SPLIT <= kGemvSlots * 32 && tune("gemv.variant", 1) == 1;
+    const bool unit = (kv + SPLIT - 1) / SPLIT <= kGemvSlots * 32 && tune("gemv.variant", 1) != 2;
     auto kern = unit ? gemv_w8a16_unit_kernel<SPLIT> : gemv_w8a16_kernel<SPLIT, UNROLL>;
     const size_t smem = (size_t)kv * 16 * sizeof(float) + kGemvWarps * kGemvMaxIters * sizeof(float);
     static bool configured[2][64] = {};
@@ -234,6 +498,10 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
     if (K > 45000) return NMT_ERR_UNSUPPORTED;                        // x must fit shared memory as fp32
     const int kv = static_cast<int>(K / 16);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (tune("gemv.variant", 3) == 3) {          // 3 = tensor-core inner product (default), 1 / 2 = CUDA-core kernels
+        const int r = launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), st);
+        if (r != NMT_ERR_UNSUPPORTED) return r;
+    }
     // K-slices of roughly 3 KB: 1 up to K = 4096, 2 up to 8192, 4 up to 16384, 8 beyond.
     int split = tune("gemv.split", K <= 4096 ? 1 : (K <= 8192 ? 2 : (K <= 16384 ? 4 : 8)));
     if (split >= 8) return launch_gemv<8>(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), kv, st);

@@ -72,6 +72,56 @@ def test_every_e4m3_value_and_split_variants(ops):
             ops.tune(k, 0)
 
 
+def test_tensor_core_path_positions_and_codes(ops):
+    """K a multiple of 64 takes the mma.sync kernel, whose lanes visit k in a permuted order: a diagonal W against
+    an x of distinct values proves W and x use the same permutation, and every e4m3 code converts exactly."""
+    codes = torch.tensor([c for c in range(256) if (c & 0x7F) != 0x7F], dtype=torch.uint8)
+    for K in (64, 128, 448, 3136):
+        N = K
+        W = torch.zeros(N, K, dtype=torch.uint8)
+        W[torch.arange(N), torch.arange(K)] = codes[torch.arange(N) % codes.numel()]
+        W = W.view(torch.float8_e4m3fn)
+        x = (1 + (torch.arange(K) % 128).float() / 128).to(BF)           # exact in bf16 and f16, distinct within a chunk pair
+        x = x * torch.tensor([1.0, -2.0, 0.5, 4.0])[(torch.arange(K) // 128) % 4].to(BF)
+        sc = torch.ones(N)
+        got = ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()).cpu()
+        want = (W.float()[torch.arange(N), torch.arange(K)] * x.float()).to(BF)
+        assert torch.equal(got, want), K
+
+
+@pytest.mark.parametrize("scale", [1e30, 1e-30, 3e4, 2.0 ** -20])
+def test_tensor_core_path_x_magnitudes(ops, scale):
+    """x is staged as f16 times a power of two taken from max|x|: huge and tiny vectors must come out as accurately
+    as ordinary ones."""
+    g = torch.Generator().manual_seed(17)
+    N, K = 96, 3136
+    x = (torch.randn(K, generator=g) * scale).to(BF)
+    W, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
+    got = ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()).float().cpu()
+    want = og.gemv_w8a16(x, W, sc).float()
+    rep = og.ulp_report(got.to(BF), want.to(BF))
+    assert rep["mismatch_frac"] <= 0.05 and rep["max_ulp"] <= 4, rep
+
+
+@pytest.mark.parametrize("N,K", [(40, 64), (9, 192), (300, 16384), (50, 16448), (1000, 512), (17, 32704)])
+def test_tensor_core_path_slicing(ops, N, K):
+    """Shapes that exercise one chunk per row, uneven slices, the register-held and re-read x staging, many
+    k-streams per tile and ragged last tiles; every stream count the knob allows."""
+    g = torch.Generator().manual_seed(N * 7 + K)
+    x = torch.randn(K, generator=g).to(BF)
+    W, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
+    want = og.gemv_w8a16(x, W, sc)
+    try:
+        for streams in (0, 1, 2, 4, 8):
+            for chunks in (0, 2, 4):
+                ops.tune("gemv.streams", streams)
+                ops.tune("gemv.unit_chunks", chunks)
+                check(ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()), want)
+    finally:
+        ops.tune("gemv.streams", 0)
+        ops.tune("gemv.unit_chunks", 0)
+
+
 def test_against_reference_kernel(ops, ref_kernels):
     if ref_kernels is None or not hasattr(ref_kernels, "ref_gemv_fp8"):
         pytest.skip("reference gemv kernel not built")
