@@ -163,6 +163,26 @@ inline void launch_kernel(void (*kern)(KArgs...), int grid, int block, size_t sm
     cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// Same, with the grid grouped into thread-block clusters of `cluster` CTAs (grid must be a multiple of it).
+template <typename... KArgs, typename... Args>
+inline void launch_cluster_kernel(void (*kern)(KArgs...), int grid, int cluster, int block, size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(block));
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(cluster);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 inline int grid_for(int64_t work_items, int items_per_cta, int max_ctas) {
     int64_t g = (work_items + items_per_cta - 1) / items_per_cta;
     if (g < 1) g = 1;

@@ -24,6 +24,9 @@ struct Knob { const char* key; std::atomic<int> value; };
 static Knob g_knobs[] = {
     {"launch.pdl", {0}},          // 1 = launch with programmatic stream serialization (default), 2 = plain launches
     // add_rmsnorm / rmsnorm (bf16)
+    {"norm.cluster", {0}},        // RMSNorm: 0 = cluster of CTAs per row only for rows one CTA cannot hold, 2/4/8 = always, 1 = never
+    {"norm.cluster_block", {0}},  // cluster RMSNorm: threads per CTA, 512 (default) or 256
+    {"norm.cluster_ctas_per_sm", {0}},  // cluster RMSNorm: CTAs per SM the grid is sized for (default 3)
     {"norm.variant", {0}},        // 0 = default (3), 1 = warp-per-row registers, 2 = TMA-staged tiles, 3 = CTA-per-row registers
     {"norm.block", {0}},          // threads per CTA for the warp-per-row kernel
     {"norm.ctas_per_sm", {0}},    // >0: persistent grid of 148*k CTAs; 0: one pass, grid = rows/warps

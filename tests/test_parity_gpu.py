@@ -415,6 +415,33 @@ def test_cta_per_row_norm_variant(ops, block):
         ops.tune("norm.block", 0)
 
 
+@pytest.mark.parametrize("cluster", [0, 2, 4, 8])
+def test_cluster_per_row_norm_variant(ops, cluster):
+    """A thread-block cluster per row with the sum of squares reduced through distributed shared memory: the
+    automatic choice for the fused add + norm on rows one CTA cannot hold (> 32,768 wide), and forced at every
+    width and for the plain norm here."""
+    shapes = [(1, 40000), (3, 65536), (5, 100000), (2, 262144), (300, 33000)] if cluster == 0 else \
+             [(1, 3136), (7, 3136), (2051, 3136), (33, 64), (9, 8), (3, 12544), (5, 40000), (2, 32768 * cluster)]
+    try:
+        ops.tune("norm.cluster", cluster)
+        for T, cols in shapes:
+            g = torch.Generator().manual_seed(T * 37 + cols)
+            x = (2 * torch.randn(T, cols, generator=g)).to(BF)
+            r = torch.randn(T, cols, generator=g).to(BF)
+            w = og.norm_weight(cols, g)
+            want_res, want = og.add_rmsnorm_bf16(x, r, w)
+            xd = dev(x)
+            out = torch.empty_like(xd)
+            n0 = ops.launch_count()
+            ops.add_rmsnorm(xd, dev(r), dev(w), out_res=xd, out=out)          # in place on the residual stream
+            assert ops.launch_count() == n0 + 1
+            assert torch.equal(xd.cpu(), want_res), (T, cols)
+            assert_ulp(out, want, f"cluster add_rmsnorm {T}x{cols}", max_frac=0.05)
+            assert_ulp(ops.rmsnorm(dev(x), dev(w)), og.rmsnorm_bf16(x, w), f"cluster rmsnorm {T}x{cols}", max_frac=0.05)
+    finally:
+        ops.tune("norm.cluster", 0)
+
+
 def test_pybind_module_and_ctypes_mirror_on_device(ops):
     """The two Python-level drop-ins for the reference's `binding` module (compiled pybind11 and ctypes), driven
     the way engine.py drives the reference: tensors by data_ptr(), sizes as ints (engine.py:40-42, 248, 261)."""
