@@ -68,7 +68,7 @@ template <> struct ConvVec<2> {
 };
 
 template <int TIME_CHUNK, int UNROLL, int NP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, NP == 2 ? 8 : 4)     // 64 registers for the default (8-byte) form: 8 CTAs per SM instead of 7, +5 %
 conv1d_silu_split_kernel(const void* __restrict__ xv, const float* __restrict__ w, const float* __restrict__ bias,
                          ConvSplit dst, float* state_out, int cv_total, int S, int batch) {
     using V = ConvVec<NP>;

@@ -28,16 +28,24 @@ __device__ __forceinline__ float scale_from_amax(float amax) {
     if (s < 1e-10f) s = 1.f / kE4M3Max;
     return s;
 }
-__device__ __forceinline__ uint32_t quant2(float a, float b, float inv) {
-    float qa = fmaxf(-kE4M3Max, fminf(kE4M3Max, a * inv));
-    float qb = fmaxf(-kE4M3Max, fminf(kE4M3Max, b * inv));
-    return static_cast<uint32_t>(__nv_cvt_float2_to_fp8x2(make_float2(qa, qb), __NV_SATFINITE, __NV_E4M3));
+// Two values -> two e4m3 bytes.  The reference clamps to [-448, 448] with fminf / fmaxf and then converts
+// (ops/gemm.cuh:286-288); the conversion used here saturates by itself, so only the upper clamp is kept: it is
+// what turns a NaN into +448 (fminf returns its non-NaN operand), and every value the lower clamp would have
+// changed (below -448, including -inf) is saturated to -448 by the conversion.  The product runs as one f32x2
+// multiply.
+__device__ __forceinline__ uint32_t quant2(const float2& v, const float2& inv2) {
+    const float2 q = __fmul2_rn(v, inv2);
+    uint32_t r;
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; cvt.u32.u16 %0, t; }"
+        : "=r"(r) : "f"(fminf(kE4M3Max, q.y)), "f"(fminf(kE4M3Max, q.x)));
+    return r;
 }
 // Eight bf16 values (one 16-byte vector) -> eight e4m3 bytes.
 __device__ __forceinline__ uint2 quant8(const uint4& v, float inv) {
+    const float2 inv2 = make_float2(inv, inv);
     uint2 o;
-    o.x = quant2(bf16_lo(v.x), bf16_hi(v.x), inv) | (quant2(bf16_lo(v.y), bf16_hi(v.y), inv) << 16);
-    o.y = quant2(bf16_lo(v.z), bf16_hi(v.z), inv) | (quant2(bf16_lo(v.w), bf16_hi(v.w), inv) << 16);
+    o.x = quant2(unpack2(v.x), inv2) | (quant2(unpack2(v.y), inv2) << 16);
+    o.y = quant2(unpack2(v.z), inv2) | (quant2(unpack2(v.w), inv2) << 16);
     return o;
 }
 __device__ __forceinline__ void st_stream8(uint2* p, const uint2& v) {

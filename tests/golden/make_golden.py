@@ -1,8 +1,9 @@
 """Generates the golden fixtures in this directory FROM THE REFERENCE'S OWN CODE.
 
-Run in a checkout that has the reference mounted (default /root/reference):
+Run where the reference checkout is available (its location comes from --reference or the REFERENCE_ROOT
+environment variable):
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py --reference <path to nemotron_infer>
 
 Two sources, neither of which copies reference text into this repository:
 
@@ -74,7 +75,7 @@ def bits(t: torch.Tensor) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("REFERENCE_ROOT", "/root/reference"))
     a = ap.parse_args()
     torch.set_num_threads(1)          # fixed summation order for the fixtures
 
