@@ -275,18 +275,23 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
         // Default shape: about 160 threads per row (392 vectors -> 3 per thread), at most 8 vectors per thread.
         int block = tune("norm.block", 0);
         if (block <= 0) {
-            int want_slots = static_cast<int>((nv + 159) / 160);
+            // measured at 3136 columns: ~160 threads per row is best with the residual add (6 loads per thread in
+            // flight), ~96 without it (5 loads per thread; 6.73 vs 6.24 TB/s for 160 threads x 2 rows)
+            const int per_row = FUSE_ADD ? 160 : 96;
+            int want_slots = static_cast<int>((nv + per_row - 1) / per_row);
             if (want_slots > 8) want_slots = 8;
             block = static_cast<int>((nv + want_slots - 1) / want_slots);
         }
         block = block > 512 ? 512 : (block + 31) / 32 * 32;
         const int slots = static_cast<int>((nv + block - 1) / block);
         const int per_sm = tune("norm.ctas_per_sm", 0);
-        const int rows_per_cta = tune("norm.rows_per_cta", FUSE_ADD ? 1 : 2);
-        const int grid = grid_for(rows, rows_per_cta >= 2 ? 2 : 1, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);
+        const int rows_per_cta = tune("norm.rows_per_cta", 1);
+        const int rows_used = (rows_per_cta >= 4 && !FUSE_ADD && slots <= 4) ? 4 : rows_per_cta >= 2 ? 2 : 1;
+        const int grid = grid_for(rows, rows_used, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);
 #define NMT_CTAROW_CASE(S)                                                                                   \
     do {                                                                                                     \
-        if (rows_per_cta >= 2) launch_kernel(rmsnorm_ctarow_kernel<S, 2, FUSE_ADD>, grid, block, 0, st, X, R, w, OR, O, rows, (int)nv, inv_cols, eps); \
+        if (rows_per_cta >= 4 && !FUSE_ADD && S <= 4) launch_kernel(rmsnorm_ctarow_kernel<S, 4, false>, grid, block, 0, st, X, R, w, OR, O, rows, (int)nv, inv_cols, eps); \
+        else if (rows_per_cta >= 2) launch_kernel(rmsnorm_ctarow_kernel<S, 2, FUSE_ADD>, grid, block, 0, st, X, R, w, OR, O, rows, (int)nv, inv_cols, eps); \
         else launch_kernel(rmsnorm_ctarow_kernel<S, 1, FUSE_ADD>, grid, block, 0, st, X, R, w, OR, O, rows, (int)nv, inv_cols, eps);                   \
     } while (0)
         if (slots <= 1) NMT_CTAROW_CASE(1);
