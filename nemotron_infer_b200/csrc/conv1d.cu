@@ -126,7 +126,9 @@ conv1d_silu_split_kernel(const void* __restrict__ xv, const float* __restrict__ 
         // Full groups of UNROLL steps: all loads first, then a straight-line window v[0..UNROLL+2] with static
         // indices (no per-step predicate, so the window never has to be shuffled between registers).
         // (Issuing the next group's loads ahead of this group's arithmetic was tried: the extra registers cost
-        // more occupancy than the overlap gained.)
+        // more occupancy than the overlap gained.  So was a per-thread cp.async ring of 16 / 32 time steps in
+        // shared memory, which keeps 4x the bytes in flight at no register cost: bit-identical and 13-25 % slower,
+        // so the bytes in flight are not what limits this kernel.)
         for (; tb + UNROLL <= t1; tb += UNROLL) {
             VT in[UNROLL];
 #pragma unroll
