@@ -163,6 +163,18 @@ inline void launch_kernel(void (*kern)(KArgs...), int grid, int block, size_t sm
     cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
+// Threads per row of the CTA-per-row norm kernels (and of the statistics pass of the norm + quantiser, which must
+// add its partial sums in the same order to stay byte-identical with "norm, then quantise").  Measured at 3136
+// columns: ~160 threads per row is best with the residual add (6 loads per thread in flight), ~96 without it
+// (5 loads per thread; 6.73 vs 6.24 TB/s for 160 threads x 2 rows).  At most 8 vectors per thread.
+inline int default_norm_block(int64_t nv, bool fuse_add) {
+    const int per_row = fuse_add ? 160 : 96;
+    int want_slots = static_cast<int>((nv + per_row - 1) / per_row);
+    if (want_slots > 8) want_slots = 8;
+    int block = static_cast<int>((nv + want_slots - 1) / want_slots);
+    return block > 512 ? 512 : (block + 31) / 32 * 32;
+}
+
 // Same, with the grid grouped into thread-block clusters of `cluster` CTAs (grid must be a multiple of it).
 template <typename... KArgs, typename... Args>
 inline void launch_cluster_kernel(void (*kern)(KArgs...), int grid, int cluster, int block, size_t smem, cudaStream_t st, Args... args) {

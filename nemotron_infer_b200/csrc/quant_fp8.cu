@@ -319,10 +319,7 @@ static int launch_norm_quant(const void* x, const void* r, const float* w, void*
     unsigned int* amax_word = static_cast<unsigned int*>(workspace);
     float* rstd = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
     if (cudaMemsetAsync(amax_word, 0, sizeof(unsigned int), st) != cudaSuccess) return finish_launch(0);
-    int want_slots = static_cast<int>((nv + 159) / 160);      // about 160 threads per row, at most 8 vectors each
-    if (want_slots > 8) want_slots = 8;
-    int block = static_cast<int>((nv + want_slots - 1) / want_slots);
-    block = block > 512 ? 512 : (block + 31) / 32 * 32;
+    const int block = default_norm_block(nv, FUSE_ADD);
     const int slots = static_cast<int>((nv + block - 1) / block);
     const int grid = grid_for(rows, 1, 0x7fffffff);
     const int qrows = tune("quant.rows_per_cta", 2);

@@ -274,14 +274,7 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
     if (tune("norm.variant", kDefaultNormVariant) == 3 && nv <= 8 * 512) {
         // Default shape: about 160 threads per row (392 vectors -> 3 per thread), at most 8 vectors per thread.
         int block = tune("norm.block", 0);
-        if (block <= 0) {
-            // measured at 3136 columns: ~160 threads per row is best with the residual add (6 loads per thread in
-            // flight), ~96 without it (5 loads per thread; 6.73 vs 6.24 TB/s for 160 threads x 2 rows)
-            const int per_row = FUSE_ADD ? 160 : 96;
-            int want_slots = static_cast<int>((nv + per_row - 1) / per_row);
-            if (want_slots > 8) want_slots = 8;
-            block = static_cast<int>((nv + want_slots - 1) / want_slots);
-        }
+        if (block <= 0) block = default_norm_block(nv, FUSE_ADD);
         block = block > 512 ? 512 : (block + 31) / 32 * 32;
         const int slots = static_cast<int>((nv + block - 1) / block);
         const int per_sm = tune("norm.ctas_per_sm", 0);
