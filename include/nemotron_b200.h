@@ -166,6 +166,21 @@ int nmt_causal_conv1d_silu_f32(const float* x, const float* w, const float* bias
 int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale, void* y_bf16, int64_t N, int64_t K,
                    void* stream);
 
+/* The same product with the decode block's neighbours folded in, one launch instead of up to four:
+ *   norm_w != NULL      x is first replaced by rmsnorm(x) * norm_w (eps as given), the pre-norm of
+ *                       mlp_block_forward_fp8 (model/mlp_block.cuh:140) and mamba_block_decode_fp8
+ *                       (model/mamba_block.cuh:473); x must then be 16-byte aligned;
+ *   activation == 1     y = relu(y)^2 on the bf16 result, the step between up_proj and down_proj
+ *                       (model/mlp_block.cuh:145-147);
+ *   residual != NULL    y[n] += residual[n] in bf16, the block's closing add (model/mlp_block.cuh:170-172,
+ *                       model/mamba_block.cuh:512-514).
+ * Byte-identical to nmt_rmsnorm_bf16 -> nmt_gemv_w8a16 -> nmt_relu2_bf16 / nmt_add_bf16 with this library's
+ * defaults.  K % 64 == 0 and K <= 16384 (NMT_ERR_UNSUPPORTED otherwise: there is no unfused fallback inside,
+ * it would need scratch memory).  Mamba's three in_proj slices (model/mamba_block.cuh:476-481) are one call
+ * with N = INTER + CONV_DIM + H rows, since they are consecutive rows of one matrix. */
+int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, const void* W_e4m3, const float* w_scale,
+                         int activation, const void* residual_bf16, void* y_bf16, int64_t N, int64_t K, void* stream);
+
 /* ---- Per-tensor FP8 (e4m3) activation quantisation ---------------------------- */
 
 /* out_fp8 = e4m3(clamp(x / s, +-448)), s = max|x| / 448 (1/448 for an all-zero tensor), *scale_out = s.

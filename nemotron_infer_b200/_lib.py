@@ -38,6 +38,7 @@ PROTOTYPES = {
     "nmt_causal_conv1d_silu_split_bf16": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _i64, _i64, _p]),
     "nmt_causal_conv1d_silu_f32": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "nmt_gemv_w8a16": (_int, [_p, _p, _p, _p, _i64, _i64, _p]),
+    "nmt_gemv_w8a16_fused": (_int, [_p, _p, _f, _p, _p, _int, _p, _p, _i64, _i64, _p]),
     "nmt_quantize_fp8": (_int, [_p, _p, _p, _p, _i64, _p]),
     "nmt_relu2_quant_fp8": (_int, [_p, _p, _p, _p, _i64, _p]),
     "nmt_fp8_workspace_bytes": (_i64, [_i64]),

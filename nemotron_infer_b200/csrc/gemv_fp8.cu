@@ -241,10 +241,23 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// What a decode block does around its projections, folded into the GEMV: the pre-norm RMSNorm of the hidden state
+// in front (model/mlp_block.cuh:140, model/mamba_block.cuh:473), relu^2 (model/mlp_block.cuh:145-147) and the
+// residual add (model/mlp_block.cuh:170-172, model/mamba_block.cuh:512-514) behind.  Every CTA needs all of x
+// anyway, so each one normalises its own copy; the arithmetic and the order of the partial sums are those of the
+// stand-alone kernels, so the fused result is byte-identical to "norm kernel, GEMV, activation kernel, add kernel".
+struct GemvFusion {
+    const float* norm_w;          // non-null: x = rmsnorm(x) * norm_w first
+    float eps, inv_cols;
+    int norm_threads;             // threads per row of the stand-alone norm kernel (its summation order)
+    int activation;               // 1: y = relu(y)^2
+    const uint16_t* residual;     // non-null: y += residual[row]
+};
+
 template <int SPLIT, int S>           // S k-streams per tile, R = 16 / S matrix rows per tile
 __global__ void __launch_bounds__(kGemvWarps * 32)
 gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, const float* __restrict__ w_scale,
-                      __nv_bfloat16* __restrict__ y, int N, int K, int iters, int early_trigger) {
+                      __nv_bfloat16* __restrict__ y, int N, int K, int iters, int early_trigger, GemvFusion fu) {
     constexpr int R = 16 / S;
     constexpr int TILES_PER_CTA = kGemvWarps / SPLIT;
     constexpr int Q = S * SPLIT;                                   // k-slices per matrix row
@@ -340,19 +353,61 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __rest
     const uint32_t* xw = reinterpret_cast<const uint32_t*>(x);
     const int words = K / 2;
     const bool held = words <= XW * kGemvWarps * 32;               // block-uniform
+    const bool normed = fu.norm_w != nullptr;                      // block-uniform
+    uint32_t* xn = reinterpret_cast<uint32_t*>(part + (size_t)iters * kGemvWarps * 16);   // K bf16: the normalised x
+    if (normed) {
+        // The stand-alone kernel's shape (rmsnorm_ctarow_kernel, one row): norm_threads threads, thread t owns
+        // vectors t, t + norm_threads, ...; per-thread f32x2 sums, warp shuffle, then the warps in order.
+        const int nt = fu.norm_threads, nv = K / 8;
+        const uint4* xv = reinterpret_cast<const uint4*>(x);
+        uint4 a[8];
+        if (threadIdx.x < nt) {
+            float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int v = q * nt + threadIdx.x;
+                a[q] = v < nv ? ld_stream(xv + v) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                float2 pr[4];
+                unpack8x2(a[q], pr);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc = __ffma2_rn(pr[k], pr[k], acc);
+            }
+            const float ss = warp_sum(acc.x + acc.y);
+            if (lane == 0) s_red[warp] = ss;
+        }
+        __syncthreads();
+        if (threadIdx.x < nt) {
+            float total = 0.f;
+            for (int i = 0; i < nt / 32; ++i) total += s_red[i];
+            const float rstd = rsqrtf(total * fu.inv_cols + fu.eps);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int v = q * nt + threadIdx.x;
+                if (v < nv) {
+                    float2 pr[4];
+                    unpack8x2(a[q], pr);
+                    reinterpret_cast<uint4*>(xn)[v] = scale8(pr, rstd, ld_weight4(fu.norm_w + (size_t)v * 8), ld_weight4(fu.norm_w + (size_t)v * 8 + 4));
+                }
+            }
+        }
+        __syncthreads();
+    }
     uint32_t xr[XW];
     float m = 0.f;
     if (held) {
 #pragma unroll
         for (int i = 0; i < XW; ++i) {
             const int idx = threadIdx.x + i * kGemvWarps * 32;
-            xr[i] = idx < words ? __ldg(xw + idx) : 0u;
+            xr[i] = idx < words ? (normed ? xn[idx] : __ldg(xw + idx)) : 0u;
         }
 #pragma unroll
         for (int i = 0; i < XW; ++i) m = fmaxf(m, fmaxf(fabsf(bf16_lo(xr[i])), fabsf(bf16_hi(xr[i]))));
     } else {
         for (int i = threadIdx.x; i < words; i += blockDim.x) {
-            const uint32_t u = xw[i];
+            const uint32_t u = normed ? xn[i] : xw[i];
             m = fmaxf(m, fmaxf(fabsf(bf16_lo(u)), fabsf(bf16_hi(u))));
         }
     }
@@ -374,7 +429,7 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __rest
         }
     } else {
         for (int i = threadIdx.x; i < words; i += blockDim.x) {
-            const uint32_t u = xw[i];
+            const uint32_t u = normed ? xn[i] : xw[i];
             reinterpret_cast<__half2*>(xh)[i] = __floats2half2_rn(bf16_lo(u) * down, bf16_hi(u) * down);
         }
     }
@@ -410,14 +465,18 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __rest
             for (int sp = 0; sp < SPLIT; ++sp)
 #pragma unroll
                 for (int s2 = 0; s2 < S; ++s2) sum += part[((size_t)it * kGemvWarps + tc * SPLIT + sp) * 16 + s2 * R + r];
-            y[row] = __float2bfloat16_rn((sum * up) * __ldg(w_scale + row));
+            // bf16 result in the low half of a pair, so the epilogues can use the stand-alone kernels' instructions
+            uint32_t yb = pack_bf16x2((sum * up) * __ldg(w_scale + row), 0.f);
+            if (fu.activation == 1) yb = relu2_bf16x2(yb);
+            if (fu.residual) yb = add_bf16x2_rn(static_cast<uint32_t>(fu.residual[row]), yb);
+            reinterpret_cast<uint16_t*>(y)[row] = static_cast<uint16_t>(yb & 0xffffu);
         }
     }
     if (!early_trigger) pdl_trigger();
 }
 
 template <int SPLIT, int S>
-static int launch_gemv_mma(const void* x, const void* W, const float* w_scale, void* y, int N, int K, cudaStream_t st) {
+static int launch_gemv_mma(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
     constexpr int R = 16 / S, TILES_PER_CTA = kGemvWarps / SPLIT;
     auto kern = gemv_w8a16_mma_kernel<SPLIT, S>;
     const int ntiles = (N + R - 1) / R;
@@ -426,7 +485,7 @@ static int launch_gemv_mma(const void* x, const void* W, const float* w_scale, v
     int iters = (ctas_needed + kSmCount * per_sm - 1) / (kSmCount * per_sm);      // passes per CTA ...
     if (iters < 1) iters = 1;
     const int grid = (ctas_needed + iters - 1) / iters;                           // ... evenly spread over the grid
-    const size_t smem = mma_x_bytes(K) + (size_t)iters * kGemvWarps * 16 * sizeof(float);
+    const size_t smem = mma_x_bytes(K) + (size_t)iters * kGemvWarps * 16 * sizeof(float) + (fu.norm_w ? (size_t)K * 2 : 0);
     if (smem > 200 * 1024) return NMT_ERR_UNSUPPORTED;
     static bool configured[64] = {};
     int dev = 0;
@@ -436,12 +495,12 @@ static int launch_gemv_mma(const void* x, const void* W, const float* w_scale, v
         configured[dev] = true;
     }
     launch_kernel(kern, grid, kGemvWarps * 32, smem, st, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(W),
-                  w_scale, static_cast<__nv_bfloat16*>(y), N, K, iters, tune("gemv.early_trigger", 1) == 1);
+                  w_scale, static_cast<__nv_bfloat16*>(y), N, K, iters, tune("gemv.early_trigger", 1) == 1, fu);
     return finish_launch(1);
 }
 
 // Picks S * SPLIT so that a work unit is about six chunks; returns NMT_ERR_UNSUPPORTED when the shape does not fit.
-static int launch_gemv_mma_auto(const void* x, const void* W, const float* w_scale, void* y, int N, int K, cudaStream_t st) {
+static int launch_gemv_mma_auto(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
     if ((K % 64) != 0) return NMT_ERR_UNSUPPORTED;
     const int kc = K / 64;
     int q = 1;
@@ -450,7 +509,7 @@ static int launch_gemv_mma_auto(const void* x, const void* W, const float* w_sca
     const int forced = tune("gemv.streams", 0);
     int split = q >= 8 ? 8 : q, streams = q / split;
     if (forced > 0 && forced <= 8 && q % forced == 0 && q / forced <= 8) { streams = forced; split = q / forced; }
-#define NMT_MMA_CASE(SP, ST) if (split == SP && streams == ST) return launch_gemv_mma<SP, ST>(x, W, w_scale, y, N, K, st)
+#define NMT_MMA_CASE(SP, ST) if (split == SP && streams == ST) return launch_gemv_mma<SP, ST>(x, W, w_scale, y, N, K, fu, st)
     NMT_MMA_CASE(1, 1); NMT_MMA_CASE(2, 1); NMT_MMA_CASE(4, 1); NMT_MMA_CASE(8, 1);
     NMT_MMA_CASE(1, 2); NMT_MMA_CASE(2, 2); NMT_MMA_CASE(4, 2); NMT_MMA_CASE(8, 2);
     NMT_MMA_CASE(1, 4); NMT_MMA_CASE(2, 4); NMT_MMA_CASE(4, 4); NMT_MMA_CASE(8, 4);
@@ -488,6 +547,28 @@ static int launch_gemv(const void* x, const void* W, const float* w_scale, void*
 
 extern "C" {
 
+int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, const void* W_e4m3, const float* w_scale,
+                         int activation, const void* residual_bf16, void* y_bf16, int64_t N, int64_t K, void* stream) {
+    using namespace nmt;
+    if (N < 0 || K <= 0 || (K % 16) != 0 || N > 0x7fffffff || activation < 0 || activation > 1) return NMT_ERR_SHAPE;
+    if (N == 0) return NMT_OK;
+    if (!x_bf16 || !W_e4m3 || !w_scale || !y_bf16) return NMT_ERR_NULL;
+    if (!aligned4(x_bf16) || !aligned16(W_e4m3) || !aligned4(w_scale) || (reinterpret_cast<uintptr_t>(y_bf16) & 1u) ||
+        (norm_w && (!aligned16(x_bf16) || !aligned16(norm_w))) || (reinterpret_cast<uintptr_t>(residual_bf16) & 1u))
+        return NMT_ERR_ALIGN;
+    GemvFusion fu = {};
+    fu.norm_w = norm_w;
+    fu.eps = eps;
+    fu.inv_cols = 1.0f / static_cast<float>(K);
+    fu.norm_threads = default_norm_block(K / 8, false);
+    fu.activation = activation;
+    fu.residual = static_cast<const uint16_t*>(residual_bf16);
+    // The prologue keeps a thread's share of x in 8 registers-vectors; the fused forms exist only on the tensor-core kernel.
+    if (norm_w && (fu.norm_threads > kGemvWarps * 32 || (K / 8 + fu.norm_threads - 1) / fu.norm_threads > 8)) return NMT_ERR_UNSUPPORTED;
+    return launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
+                                static_cast<cudaStream_t>(stream));
+}
+
 int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale, void* y_bf16, int64_t N, int64_t K,
                    void* stream) {
     using namespace nmt;
@@ -499,7 +580,7 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
     const int kv = static_cast<int>(K / 16);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (tune("gemv.variant", 3) == 3) {          // 3 = tensor-core inner product (default), 1 / 2 = CUDA-core kernels
-        const int r = launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), st);
+        const int r = launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), GemvFusion{}, st);
         if (r != NMT_ERR_UNSUPPORTED) return r;
     }
     // K-slices of roughly 3 KB: 1 up to K = 4096, 2 up to 8192, 4 up to 16384, 8 beyond.

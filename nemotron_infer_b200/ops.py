@@ -201,6 +201,31 @@ def gemv_w8a16(x: torch.Tensor, W: torch.Tensor, w_scale: torch.Tensor, out: tor
     return out
 
 
+def gemv_w8a16_fused(x: torch.Tensor, W: torch.Tensor, w_scale: torch.Tensor, norm_w: torch.Tensor | None = None,
+                     eps: float = 1e-5, activation: str | None = None, residual: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """The decode projection with its neighbours folded in: y = W @ (rmsnorm(x) * norm_w if norm_w is given else x)
+    * w_scale, then relu^2 (activation="relu2"), then + residual - one launch, byte-identical to the separate ops."""
+    N, K = W.shape
+    out = torch.empty(N, dtype=torch.bfloat16, device=x.device) if out is None else out
+    _dev(x, W, w_scale, out)
+    if W.dtype != torch.float8_e4m3fn or x.dtype != torch.bfloat16 or w_scale.dtype != torch.float32 or out.dtype != torch.bfloat16:
+        raise ValueError("W must be float8_e4m3fn, x and out bf16, w_scale fp32")
+    if x.numel() != K or w_scale.numel() != N or out.numel() != N:
+        raise ValueError("shape mismatch")
+    if norm_w is not None and (norm_w.dtype != torch.float32 or norm_w.numel() != K or not norm_w.is_cuda):
+        raise ValueError("norm_w must be fp32 [K] on the device")
+    if residual is not None and (residual.dtype != torch.bfloat16 or residual.numel() != N or not residual.is_cuda):
+        raise ValueError("residual must be bf16 [N] on the device")
+    if activation not in (None, "relu2"):
+        raise ValueError("activation must be None or 'relu2'")
+    _lib.check(_lib.load().nmt_gemv_w8a16_fused(x.data_ptr(), norm_w.data_ptr() if norm_w is not None else None, float(eps),
+                                                W.data_ptr(), w_scale.data_ptr(), 1 if activation == "relu2" else 0,
+                                                residual.data_ptr() if residual is not None else None, out.data_ptr(), N, K,
+                                                _stream()), "gemv_w8a16_fused")
+    return out
+
+
 def _fp8_out(like: torch.Tensor, out: torch.Tensor | None) -> torch.Tensor:
     out = torch.empty(like.shape, dtype=torch.float8_e4m3fn, device=like.device) if out is None else out
     if out.dtype != torch.float8_e4m3fn or out.shape != like.shape:

@@ -122,6 +122,54 @@ def test_tensor_core_path_slicing(ops, N, K):
         ops.tune("gemv.unit_chunks", 0)
 
 
+@pytest.mark.parametrize("N,K", [(12544, 3136), (3136, 12544), (17504, 3136), (3136, 7680), (40, 64), (16, 16384)])
+def test_fused_decode_forms_are_byte_identical_to_the_separate_ops(ops, N, K):
+    """norm -> GEMV -> relu^2 / residual add as one launch: same bytes as this library's separate kernels, and the
+    oracle's composition of the same steps within the GEMV tolerance."""
+    g = torch.Generator().manual_seed(N + 3 * K)
+    x = (2 * torch.randn(K, generator=g)).to(BF)
+    nw = og.norm_weight(K, g)
+    W, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
+    res = torch.randn(N, generator=g).to(BF)
+    xd, nwd, Wd, scd, resd = x.cuda(), nw.cuda(), W.cuda(), sc.cuda(), res.cuda()
+    normed = ops.rmsnorm(xd.view(1, K), nwd).view(K)
+    y_plain = ops.gemv_w8a16(normed, Wd, scd)
+    cases = {
+        "norm": (dict(norm_w=nwd), y_plain),
+        "norm+relu2": (dict(norm_w=nwd, activation="relu2"), ops.relu2(y_plain)),
+        "residual": (dict(residual=resd), ops.add(resd, ops.gemv_w8a16(xd, Wd, scd))),
+        "relu2": (dict(activation="relu2"), ops.relu2(ops.gemv_w8a16(xd, Wd, scd))),
+        "norm+relu2+residual": (dict(norm_w=nwd, activation="relu2", residual=resd), ops.add(resd, ops.relu2(y_plain))),
+    }
+    for name, (kw, want) in cases.items():
+        n0 = ops.launch_count()
+        got = ops.gemv_w8a16_fused(xd, Wd, scd, **kw)
+        assert ops.launch_count() == n0 + 1, name
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), name
+    # oracle composition (torch golden formulation of each step)
+    # (the norm may sit one bf16 ulp from the golden's in a few elements, which a nearly cancelling row sum
+    # magnifies in ulps, so only the reference test's absolute / relative bar applies here)
+    want_n = og.rmsnorm_bf16(x.view(1, K), nw).view(K)
+    want_y = og.gemv_w8a16(want_n, W, sc).float()
+    got_y = ops.gemv_w8a16_fused(xd, Wd, scd, norm_w=nwd).float().cpu()
+    assert bool(((got_y - want_y).abs() <= torch.maximum(torch.full_like(want_y, 0.02), 0.02 * want_y.abs())).all())
+    want_mlp = og.relu2_bf16(og.gemv_w8a16(want_n, W, sc).to(BF))
+    got_mlp = ops.gemv_w8a16_fused(xd, Wd, scd, norm_w=nwd, activation="relu2").float().cpu()
+    tol = torch.maximum(torch.full_like(want_mlp.float(), 0.02), 0.04 * want_mlp.float().abs())     # the square doubles the relative error
+    assert bool(((got_mlp - want_mlp.float()).abs() <= tol).all())
+
+
+def test_fused_gemv_argument_checks(built_lib):
+    L = built_lib
+    B = 0x7F0000000000
+    assert L.nmt_gemv_w8a16_fused(B, B, 1e-5, B, B, 0, B, B, 0, 3136, None) == 0          # N == 0: nothing to do
+    assert L.nmt_gemv_w8a16_fused(B, B, 1e-5, B, B, 2, B, B, 4, 3136, None) == 3          # unknown activation
+    assert L.nmt_gemv_w8a16_fused(B, B, 1e-5, None, B, 0, B, B, 4, 3136, None) == 1
+    assert L.nmt_gemv_w8a16_fused(B + 4, B, 1e-5, B, B, 0, None, B, 4, 3136, None) == 2   # norm prologue wants 16-byte x
+    assert L.nmt_gemv_w8a16_fused(B, None, 1e-5, B, B, 0, None, B, 4, 3152, None) == 5    # K % 64 != 0: no fused form
+    assert L.nmt_gemv_w8a16_fused(B, B, 1e-5, B, B, 0, None, B, 4, 32768, None) == 5      # norm prologue beyond 16384
+
+
 def test_against_reference_kernel(ops, ref_kernels):
     if ref_kernels is None or not hasattr(ref_kernels, "ref_gemv_fp8"):
         pytest.skip("reference gemv kernel not built")
