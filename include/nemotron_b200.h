@@ -152,6 +152,15 @@ int nmt_causal_conv1d_silu_split_bf16(const void* xbc, const float* w, const flo
                                       void* out2, int64_t n0, int64_t n1, int64_t n2, float* state_out,
                                       int64_t S, int64_t batch, void* stream);
 
+/* The single-token step of the same op: xbc is [batch, conv_dim] bf16 (one new row per sequence), state is the
+ * [batch, conv_dim, 3] fp32 window (read, shifted, written back - the tensor the prefill call leaves in
+ * state_out), the output goes straight into the x | B | C tensors ([batch, n_i] each).  Replaces
+ * causal_conv1d_decode_bf16 (ops/mamba2/causal_conv1d.cuh:391-456) and the three strided copies after it
+ * (model/mamba_block.cuh:487-497).  state must be 16-byte aligned. */
+int nmt_causal_conv1d_silu_decode_split_bf16(const void* xbc, const float* w, const float* bias, void* out0, void* out1,
+                                             void* out2, int64_t n0, int64_t n1, int64_t n2, float* state, int64_t batch,
+                                             void* stream);
+
 /* fp32 twin, unsplit; replaces causal_conv1d_prefill_fp32 (ops/mamba2/causal_conv1d.cuh:115-127). */
 int nmt_causal_conv1d_silu_f32(const float* x, const float* w, const float* bias, float* y, float* state_out,
                                int64_t conv_dim, int64_t S, int64_t batch, void* stream);

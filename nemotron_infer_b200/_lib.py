@@ -36,6 +36,7 @@ PROTOTYPES = {
     "nmt_embedding_bf16_i64": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _p]),
     "nmt_embedding_bf16_i32": (_int, [_p, _p, _p, _i64, _i64, _i64, _p, _p]),
     "nmt_causal_conv1d_silu_split_bf16": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _i64, _i64, _p]),
+    "nmt_causal_conv1d_silu_decode_split_bf16": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _i64, _p]),
     "nmt_causal_conv1d_silu_f32": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "nmt_gemv_w8a16": (_int, [_p, _p, _p, _p, _i64, _i64, _p]),
     "nmt_gemv_w8a16_fused": (_int, [_p, _p, _f, _p, _p, _int, _p, _p, _i64, _i64, _p]),

@@ -172,6 +172,47 @@ conv1d_silu_split_kernel(const void* __restrict__ xv, const float* __restrict__ 
     pdl_trigger();
 }
 
+// Single-token form: one new xBC row per sequence, the three previous inputs come from (and the window goes back
+// to) the fp32 state [batch, conv_dim, 3] that the prefill kernel left behind.  A thread owns 4 channels: 8 bytes of
+// x, 48 contiguous bytes of state (three float4), 8 bytes of output stored straight into its x | B | C segment.
+__global__ void __launch_bounds__(128)
+conv1d_silu_decode_split_kernel(const uint2* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
+                                ConvSplit dst, float* state, int cv_total, int batch) {
+    pdl_wait();
+    const int cv = blockIdx.x * blockDim.x + threadIdx.x;          // which 4-channel vector
+    const int b = blockIdx.y;
+    if (cv < cv_total) {
+        const uint2 xv = x[(size_t)b * cv_total + cv];
+        const float xin[4] = {bf16_lo(xv.x), bf16_hi(xv.x), bf16_lo(xv.y), bf16_hi(xv.y)};
+        float4* sp = reinterpret_cast<float4*>(state + ((size_t)b * cv_total + cv) * 4 * (kConvTaps - 1));
+        const float4 s0 = sp[0], s1 = sp[1], s2 = sp[2];
+        const float st[12] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w, s2.x, s2.y, s2.z, s2.w};   // [channel][3]
+        float o[4], ns[12];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float4 wt = ld_weight4(w + ((size_t)cv * 4 + c) * kConvTaps);
+            float acc = __ldg(bias + cv * 4 + c);                   // bias, then taps oldest to newest (causal_conv1d.cuh:415-418)
+            acc = fmaf(wt.x, st[3 * c], acc);
+            acc = fmaf(wt.y, st[3 * c + 1], acc);
+            acc = fmaf(wt.z, st[3 * c + 2], acc);
+            acc = fmaf(wt.w, xin[c], acc);
+            o[c] = silu_fast(acc);
+            ns[3 * c] = st[3 * c + 1];
+            ns[3 * c + 1] = st[3 * c + 2];
+            ns[3 * c + 2] = xin[c];
+        }
+        sp[0] = make_float4(ns[0], ns[1], ns[2], ns[3]);
+        sp[1] = make_float4(ns[4], ns[5], ns[6], ns[7]);
+        sp[2] = make_float4(ns[8], ns[9], ns[10], ns[11]);
+        int seg = 0, col = cv;                                      // segment widths are in units of 8 channels = 2 vectors
+        if (col >= dst.nv[0] * 2) { col -= dst.nv[0] * 2; seg = 1; if (col >= dst.nv[1] * 2) { col -= dst.nv[1] * 2; seg = 2; } }
+        uint2* outp = reinterpret_cast<uint2*>(seg == 0 ? dst.out[0] : seg == 1 ? dst.out[1] : dst.out[2]);
+        const int onv = (seg == 0 ? dst.nv[0] : seg == 1 ? dst.nv[1] : dst.nv[2]) * 2;
+        outp[(size_t)b * onv + col] = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+    }
+    pdl_trigger();
+}
+
 // fp32 twin (parity with the golden emitter's stage tensors): one thread per (channel, chunk), scalar.
 __global__ void __launch_bounds__(128)
 conv1d_silu_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
@@ -252,6 +293,35 @@ int nmt_causal_conv1d_silu_split_bf16(const void* xbc, const float* w, const flo
     else if (time_chunk == 8) NMT_CONV_CASE(8, 4);
     else NMT_CONV_CASE(4, 4);
 #undef NMT_CONV_CASE
+    return finish_launch(1);
+}
+
+int nmt_causal_conv1d_silu_decode_split_bf16(const void* xbc, const float* w, const float* bias, void* out0, void* out1,
+                                             void* out2, int64_t n0, int64_t n1, int64_t n2, float* state, int64_t batch,
+                                             void* stream) {
+    using namespace nmt;
+    if (batch < 0 || n0 <= 0 || n1 < 0 || n2 < 0 || (n0 % 8) || (n1 % 8) || (n2 % 8)) return NMT_ERR_SHAPE;
+    if (batch == 0) return NMT_OK;
+    if (!xbc || !w || !bias || !state || !out0 || (n1 > 0 && !out1) || (n2 > 0 && !out2)) return NMT_ERR_NULL;
+    if (!aligned16(xbc) || !aligned16(w) || !aligned4(bias) || !aligned16(state) || !aligned16(out0) ||
+        (n1 > 0 && !aligned16(out1)) || (n2 > 0 && !aligned16(out2)))
+        return NMT_ERR_ALIGN;
+    if (batch > 65535) return NMT_ERR_UNSUPPORTED;
+    ConvSplit dst;
+    dst.out[0] = static_cast<uint4*>(out0); dst.out[1] = static_cast<uint4*>(out1); dst.out[2] = static_cast<uint4*>(out2);
+    dst.nv[0] = static_cast<int>(n0 / 8); dst.nv[1] = static_cast<int>(n1 / 8); dst.nv[2] = static_cast<int>(n2 / 8);
+    const int cv_total = (dst.nv[0] + dst.nv[1] + dst.nv[2]) * 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((cv_total + 127) / 128, static_cast<unsigned>(batch));
+    cfg.blockDim = dim3(128);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, conv1d_silu_decode_split_kernel, static_cast<const uint2*>(xbc), w, bias, dst, state, cv_total,
+                       static_cast<int>(batch));
     return finish_launch(1);
 }
 

@@ -187,6 +187,30 @@ def causal_conv1d_silu(xbc: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, s
     return (res, state) if return_state else res
 
 
+def causal_conv1d_silu_decode(xbc: torch.Tensor, w: torch.Tensor, bias: torch.Tensor, state: torch.Tensor,
+                              split: tuple[int, ...] | None = None):
+    """One decode step of the causal conv1d + SiLU: xbc [batch, conv_dim] bf16, state [batch, conv_dim, 3] fp32
+    (updated in place).  Returns the bf16 result, as three tensors when split=(n0, n1, n2) is given."""
+    if xbc.dim() != 2 or xbc.dtype != torch.bfloat16:
+        raise ValueError("xbc must be bf16 [batch, conv_dim]")
+    batch, C = xbc.shape
+    _dev(xbc, w, bias, state)
+    if w.dtype != torch.float32 or bias.dtype != torch.float32 or w.numel() != C * 4 or bias.numel() != C:
+        raise ValueError("w must be fp32 [conv_dim, 4] and bias fp32 [conv_dim]")
+    if state.dtype != torch.float32 or tuple(state.shape) != (batch, C, 3) or not state.is_contiguous():
+        raise ValueError("state must be contiguous fp32 [batch, conv_dim, 3]")
+    sizes = tuple(split) if split is not None else (C,)
+    if sum(sizes) != C or len(sizes) > 3:
+        raise ValueError("split must be up to three sizes that add up to conv_dim")
+    outs = [torch.empty(batch, n, dtype=torch.bfloat16, device=xbc.device) for n in sizes]
+    ptrs = [o.data_ptr() for o in outs] + [None] * (3 - len(outs))
+    ns = list(sizes) + [0] * (3 - len(sizes))
+    _lib.check(_lib.load().nmt_causal_conv1d_silu_decode_split_bf16(xbc.data_ptr(), w.data_ptr(), bias.data_ptr(), ptrs[0], ptrs[1],
+                                                                    ptrs[2], ns[0], ns[1], ns[2], state.data_ptr(), batch, _stream()),
+               "causal_conv1d_silu_decode")
+    return outs if split is not None else outs[0]
+
+
 def gemv_w8a16(x: torch.Tensor, W: torch.Tensor, w_scale: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """y[N] = (W[N, K] (e4m3) @ x[K] (bf16)) * w_scale[N], fp32 accumulation, bf16 result: the decode projection."""
     N, K = W.shape

@@ -109,6 +109,18 @@ def conv_state_tail(x: torch.Tensor, K: int = 4) -> torch.Tensor:
 
 # --- W8A16 GEMV (tests/ops/test_gemm.cu:505-531: gemv_fp8_ref and quant_weight_perrow) -------------------------
 
+def causal_conv1d_decode_bf16(x_t: torch.Tensor, w: torch.Tensor, b: torch.Tensor, state: torch.Tensor):
+    """One decode step (ops/mamba2/causal_conv1d.cuh:409-429): x_t [batch, C] bf16, state [batch, C, K-1] fp32.
+    acc = b + sum_k w[:, k] * state[..., k] + w[:, K-1] * x_t; returns (silu(acc) as bf16, shifted state)."""
+    xf = x_t.float()
+    acc = b.expand_as(xf).clone()
+    for k in range(w.shape[1] - 1):
+        acc = acc + w[:, k] * state[..., k]
+    acc = acc + w[:, -1] * xf
+    new_state = torch.cat([state[..., 1:], xf.unsqueeze(-1)], dim=-1)
+    return F.silu(acc).to(torch.bfloat16), new_state
+
+
 def quant_weight_perrow(Wf: torch.Tensor):
     """Per-output-row e4m3 quantisation of an fp32 weight matrix: (W_e4m3, w_scale)."""
     amax = Wf.abs().amax(dim=1)

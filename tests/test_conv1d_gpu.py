@@ -53,6 +53,44 @@ def test_bf16_conv_against_golden(ops, batch, S, C, split):
     assert torch.equal(whole.view(torch.int16), got.view(torch.int16))
 
 
+@pytest.mark.parametrize("batch,C,split", [(1, 9728, (7680, 1024, 1024)), (3, 9728, (7680, 1024, 1024)), (2, 64, None), (1, 8, None),
+                                           (5, 256, (8, 248))])
+def test_decode_step_continues_the_prefill(ops, batch, C, split):
+    """Prefill S tokens, then feed the next tokens one at a time through the decode step: every step must match the
+    golden step formula on the carried state AND the prefill over the longer sequence (the same causal window)."""
+    S, steps = 37, 6
+    x, w, b = make(batch, S + steps, C, seed=11)
+    xd, wd, bd = x.cuda(), w.cuda(), b.cuda()
+    _, state = ops.causal_conv1d_silu(xd[:, :S].contiguous(), wd, bd, return_state=True)
+    want_all = og.causal_conv1d_silu_bf16(x, w, b)
+    ostate = og.conv_state_tail(x[:, :S])
+    for t in range(S, S + steps):
+        xt = xd[:, t].contiguous()
+        out = ops.causal_conv1d_silu_decode(xt, wd, bd, state, split=split)
+        got = torch.cat([o.cpu() for o in out], dim=-1) if split is not None else out.cpu()
+        want_step, ostate = og.causal_conv1d_decode_bf16(x[:, t], w, b, ostate)
+        for want in (want_step, want_all[:, t]):
+            # one bf16 ulp, except where the taps nearly cancel: there the fp32 sum's last bits (fma or not, order)
+            # are many ulps of a tiny result, so those elements get an absolute bar instead
+            big = want.float().abs() >= 1e-2
+            rep = og.ulp_report(got[big], want[big])
+            assert rep["max_ulp"] <= 1 and rep["mismatch_frac"] <= 0.02, (t, rep)
+            assert float((got.float() - want.float())[~big].abs().max()) <= 1e-4 if bool((~big).any()) else True
+        assert torch.equal(state.cpu(), ostate), t                   # the window holds raw inputs: exact
+    assert torch.equal(state.cpu(), og.conv_state_tail(x))
+
+
+def test_decode_step_argument_checks(built_lib):
+    L = built_lib
+    B = 0x7F0000000000
+    f = L.nmt_causal_conv1d_silu_decode_split_bf16
+    assert f(B, B, B, B, B, B, 7680, 1024, 1024, B, 0, None) == 0          # empty batch
+    assert f(B, B, B, B, B, B, 7684, 1024, 1024, B, 1, None) == 3          # segment not a multiple of 8 channels
+    assert f(B, B, B, B, B, B, 7680, 1024, 1024, None, 1, None) == 1       # the state is not optional here
+    assert f(B, B, B, B, B, B, 7680, 1024, 1024, B + 4, 1, None) == 2      # state must be 16-byte aligned
+    assert f(B, B, B, B, None, B, 7680, 1024, 1024, B, 1, None) == 1       # a non-empty segment needs its tensor
+
+
 def test_conv_against_reference_kernel(ops, ref_kernels):
     if ref_kernels is None or not hasattr(ref_kernels, "ref_causal_conv1d_bf16"):
         pytest.skip("reference conv1d kernel not built")
