@@ -345,6 +345,18 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> dict | None:
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    if world == 1:
+        # BASELINE.json configs[1..3] (and the gather) at their own sizes, each op alone: batches of 10 back-to-back
+        # launches over rotating buffer sets larger than L2, CUDA events, median of 10 batches.
+        from nemotron_infer_b200 import microbench as mb
+        per_op = {}
+        for op, tok in (("add_rmsnorm", 8192), ("gated", 16384), ("relu2", 8192), ("embedding", 65536)):
+            r = mb.run_op(op, tok, 10, 3, f"cuda:{local_rank}", 10, False)
+            per_op[op] = {"tokens": tok, "us_per_launch": r["median_us"], "achieved_gbs": r["gbs"],
+                          "frac_of_measured_peak": round(r["gbs"] / peak, 4),
+                          "frac_of_nominal_8000": round(r["gbs"] / NOMINAL_HBM_GBS, 4), "tokens_per_s": r["tokens_per_s"]}
+            torch.cuda.empty_cache()
+        out["ops_at_config_sizes"] = per_op
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         v, ms = cpu_chain_tokens_per_s(args.cpu_tokens, 3, threads)
