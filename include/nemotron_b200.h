@@ -185,7 +185,8 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
  *                       model/mamba_block.cuh:512-514).
  * Byte-identical to nmt_rmsnorm_bf16 -> nmt_gemv_w8a16 -> nmt_relu2_bf16 / nmt_add_bf16 with this library's
  * defaults.  K % 64 == 0 and K <= 16384 (NMT_ERR_UNSUPPORTED otherwise: there is no unfused fallback inside,
- * it would need scratch memory).  Mamba's three in_proj slices (model/mamba_block.cuh:476-481) are one call
+ * it would need scratch memory).  y may alias residual (each element is read, then written, by one thread) but
+ * not x.  Mamba's three in_proj slices (model/mamba_block.cuh:476-481) are one call
  * with N = INTER + CONV_DIM + H rows, since they are consecutive rows of one matrix. */
 int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, const void* W_e4m3, const float* w_scale,
                          int activation, const void* residual_bf16, void* y_bf16, int64_t N, int64_t K, void* stream);

@@ -146,6 +146,9 @@ def test_fused_decode_forms_are_byte_identical_to_the_separate_ops(ops, N, K):
         got = ops.gemv_w8a16_fused(xd, Wd, scd, **kw)
         assert ops.launch_count() == n0 + 1, name
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), name
+    buf = resd.clone()                                   # the residual stream updated in place
+    ops.gemv_w8a16_fused(xd, Wd, scd, residual=buf, out=buf)
+    assert torch.equal(buf.view(torch.int16), cases["residual"][1].view(torch.int16))
     # oracle composition (torch golden formulation of each step)
     # (the norm may sit one bf16 ulp from the golden's in a few elements, which a nearly cancelling row sum
     # magnifies in ulps, so only the reference test's absolute / relative bar applies here)
