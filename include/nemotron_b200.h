@@ -184,7 +184,7 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
  *   residual != NULL    y[n] += residual[n] in bf16, the block's closing add (model/mlp_block.cuh:170-172,
  *                       model/mamba_block.cuh:512-514).
  * Byte-identical to nmt_rmsnorm_bf16 -> nmt_gemv_w8a16 -> nmt_relu2_bf16 / nmt_add_bf16 with this library's
- * defaults.  K % 64 == 0 and K <= 16384 (NMT_ERR_UNSUPPORTED otherwise: there is no unfused fallback inside,
+ * defaults.  K % 64 == 0, and K <= 10240 when norm_w is given (NMT_ERR_UNSUPPORTED otherwise: there is no unfused fallback inside,
  * it would need scratch memory).  y may alias residual (each element is read, then written, by one thread) but
  * not x.  Mamba's three in_proj slices (model/mamba_block.cuh:476-481) are one call
  * with N = INTER + CONV_DIM + H rows, since they are consecutive rows of one matrix. */

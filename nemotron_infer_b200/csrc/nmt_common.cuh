@@ -164,15 +164,16 @@ inline void launch_kernel(void (*kern)(KArgs...), int grid, int block, size_t sm
 }
 
 // Threads per row of the CTA-per-row norm kernels (and of the statistics pass of the norm + quantiser, which must
-// add its partial sums in the same order to stay byte-identical with "norm, then quantise").  Measured at 3136
-// columns: ~160 threads per row is best with the residual add (6 loads per thread in flight), ~96 without it
-// (5 loads per thread; 6.73 vs 6.24 TB/s for 160 threads x 2 rows).  At most 8 vectors per thread.
+// add its partial sums in the same order to stay byte-identical with "norm, then quantise").  Measured from 3136
+// to 32,768 columns: about 3 vectors per thread is best with the residual add (6 loads per thread in flight),
+// about 5 without it - 3136 columns: 160 / 96 threads (plain norm 6.73 vs 6.24 TB/s for 160 threads x 2 rows),
+// 12,544 columns: 512 / 320 threads (plain norm 6.16 vs 4.85 TB/s at 224).  At most 512 threads, so up to 8
+// vectors per thread at the 32,768-column limit of these kernels.
 inline int default_norm_block(int64_t nv, bool fuse_add) {
-    const int per_row = fuse_add ? 160 : 96;
-    int want_slots = static_cast<int>((nv + per_row - 1) / per_row);
-    if (want_slots > 8) want_slots = 8;
-    int block = static_cast<int>((nv + want_slots - 1) / want_slots);
-    return block > 512 ? 512 : (block + 31) / 32 * 32;
+    const int per_thread = fuse_add ? 3 : 5;
+    int64_t block = (nv + per_thread - 1) / per_thread;
+    block = (block + 31) / 32 * 32;
+    return block > 512 ? 512 : static_cast<int>(block);
 }
 
 // Same, with the grid grouped into thread-block clusters of `cluster` CTAs (grid must be a multiple of it).

@@ -262,12 +262,10 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
         const int s = launch_norm_tma(FUSE_ADD, x, r, w, out_res, out, rows, cols, eps, st);
         if (s != NMT_ERR_UNSUPPORTED) return s;
     }
-    // norm.cluster: 0 = a cluster of CTAs per row where one CTA cannot hold the row and the residual add is fused
-    // (measured: 5.8 vs 5.0 TB/s at 65,536 columns; without the add the two-pass kernel, whose second read of the
-    // row mostly hits L2, is the faster one), 2 / 4 / 8 = that cluster size for every width and both forms,
-    // 1 = never.
+    // norm.cluster: 0 = a cluster of CTAs per row where one CTA cannot hold the row in registers (more than 32,768
+    // columns), 2 / 4 / 8 = that cluster size for every width, 1 = never (wide rows take the two-pass kernel).
     const int cluster = tune("norm.cluster", 0);
-    if (cluster >= 2 || (cluster == 0 && FUSE_ADD && nv > 8 * 512)) {
+    if (cluster >= 2 || (cluster == 0 && nv > 8 * 512)) {
         const int s = launch_norm_cluster(FUSE_ADD, x, r, w, out_res, out, rows, cols, eps, cluster, st);
         if (s != NMT_ERR_UNSUPPORTED) return s;
     }

@@ -122,7 +122,7 @@ def test_tensor_core_path_slicing(ops, N, K):
         ops.tune("gemv.unit_chunks", 0)
 
 
-@pytest.mark.parametrize("N,K", [(12544, 3136), (3136, 12544), (17504, 3136), (3136, 7680), (40, 64), (16, 16384)])
+@pytest.mark.parametrize("N,K", [(12544, 3136), (3136, 12544), (17504, 3136), (3136, 7680), (40, 64), (16, 10240)])
 def test_fused_decode_forms_are_byte_identical_to_the_separate_ops(ops, N, K):
     """norm -> GEMV -> relu^2 / residual add as one launch: same bytes as this library's separate kernels, and the
     oracle's composition of the same steps within the GEMV tolerance."""
@@ -141,7 +141,10 @@ def test_fused_decode_forms_are_byte_identical_to_the_separate_ops(ops, N, K):
         "relu2": (dict(activation="relu2"), ops.relu2(ops.gemv_w8a16(xd, Wd, scd))),
         "norm+relu2+residual": (dict(norm_w=nwd, activation="relu2", residual=resd), ops.add(resd, ops.relu2(y_plain))),
     }
+    with_norm = K <= 10240                               # the norm prologue exists up to 10,240 columns (the model norms 3136)
     for name, (kw, want) in cases.items():
+        if "norm" in name and not with_norm:
+            continue
         n0 = ops.launch_count()
         got = ops.gemv_w8a16_fused(xd, Wd, scd, **kw)
         assert ops.launch_count() == n0 + 1, name
@@ -152,6 +155,8 @@ def test_fused_decode_forms_are_byte_identical_to_the_separate_ops(ops, N, K):
     # oracle composition (torch golden formulation of each step)
     # (the norm may sit one bf16 ulp from the golden's in a few elements, which a nearly cancelling row sum
     # magnifies in ulps, so only the reference test's absolute / relative bar applies here)
+    if not with_norm:
+        return
     want_n = og.rmsnorm_bf16(x.view(1, K), nw).view(K)
     want_y = og.gemv_w8a16(want_n, W, sc).float()
     got_y = ops.gemv_w8a16_fused(xd, Wd, scd, norm_w=nwd).float().cpu()
@@ -170,7 +175,7 @@ def test_fused_gemv_argument_checks(built_lib):
     assert L.nmt_gemv_w8a16_fused(B, B, 1e-5, None, B, 0, B, B, 4, 3136, None) == 1
     assert L.nmt_gemv_w8a16_fused(B + 4, B, 1e-5, B, B, 0, None, B, 4, 3136, None) == 2   # norm prologue wants 16-byte x
     assert L.nmt_gemv_w8a16_fused(B, None, 1e-5, B, B, 0, None, B, 4, 3152, None) == 5    # K % 64 != 0: no fused form
-    assert L.nmt_gemv_w8a16_fused(B, B, 1e-5, B, B, 0, None, B, 4, 32768, None) == 5      # norm prologue beyond 16384
+    assert L.nmt_gemv_w8a16_fused(B, B, 1e-5, B, B, 0, None, B, 4, 12544, None) == 5      # norm prologue beyond 10240 columns
 
 
 def test_against_reference_kernel(ops, ref_kernels):

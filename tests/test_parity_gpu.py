@@ -415,8 +415,9 @@ def test_cta_per_row_norm_variant(ops, block):
         ops.tune("norm.block", 0)
 
 
+@pytest.mark.parametrize("staged", [1, 2])
 @pytest.mark.parametrize("cluster", [0, 2, 4, 8])
-def test_cluster_per_row_norm_variant(ops, cluster):
+def test_cluster_per_row_norm_variant(ops, built_lib, cluster, staged):
     """A thread-block cluster per row with the sum of squares reduced through distributed shared memory: the
     automatic choice for the fused add + norm on rows one CTA cannot hold (> 32,768 wide), and forced at every
     width and for the plain norm here."""
@@ -424,6 +425,7 @@ def test_cluster_per_row_norm_variant(ops, cluster):
              [(1, 3136), (7, 3136), (2051, 3136), (33, 64), (9, 8), (3, 12544), (5, 40000), (2, 32768 * cluster)]
     try:
         ops.tune("norm.cluster", cluster)
+        ops.tune("norm.cluster_staged", staged)      # 1 = row shares staged in shared memory by bulk copies, 2 = registers only
         for T, cols in shapes:
             g = torch.Generator().manual_seed(T * 37 + cols)
             x = (2 * torch.randn(T, cols, generator=g)).to(BF)
@@ -438,8 +440,11 @@ def test_cluster_per_row_norm_variant(ops, cluster):
             assert torch.equal(xd.cpu(), want_res), (T, cols)
             assert_ulp(out, want, f"cluster add_rmsnorm {T}x{cols}", max_frac=0.05)
             assert_ulp(ops.rmsnorm(dev(x), dev(w)), og.rmsnorm_bf16(x, w), f"cluster rmsnorm {T}x{cols}", max_frac=0.05)
+        torch.cuda.synchronize()
+        assert built_lib.nmt_device_wait_timeouts() == 0
     finally:
         ops.tune("norm.cluster", 0)
+        ops.tune("norm.cluster_staged", 0)
 
 
 def test_pybind_module_and_ctypes_mirror_on_device(ops):
