@@ -35,6 +35,9 @@ SHAPES = {
     "relu2": (8192, 2 * 12544 * 2),
     "add": (8192, 3 * 3136 * 2),
     "embedding": (65536, 2 * 3136 * 2 + 4),
+    # rows too wide for one CTA's registers (not a model shape): bulk-staged row shares + cluster reduction
+    "add_rmsnorm_wide": (2048, 4 * 65536 * 2),
+    "rmsnorm_wide": (2048, 2 * 65536 * 2),
     "conv1d_split": (16384, 9728 * (2 + 2)),                     # xBC in, x | B | C out (Mamba-2 conv1d + SiLU)
     # single-token decode projections (weight streaming): "tokens" is the number of output rows N here
     "gemv_up": (12544, 3136),        # up_proj   N = 12544, K = 3136: 3136 weight bytes per output row
@@ -57,13 +60,14 @@ def measured_peak() -> float | None:
 
 def make_case(op: str, T: int, dev):
     rn = lambda *s: torch.randn(*s, device=dev)  # noqa: E731
-    if op in ("add_rmsnorm", "rmsnorm", "add"):
-        x, r = rn(T, 3136).to(BF), rn(T, 3136).to(BF)
-        w = 1 + 0.1 * rn(3136)
+    if op in ("add_rmsnorm", "rmsnorm", "add", "add_rmsnorm_wide", "rmsnorm_wide"):
+        cols = 65536 if op.endswith("_wide") else 3136
+        x, r = rn(T, cols).to(BF), rn(T, cols).to(BF)
+        w = 1 + 0.1 * rn(cols)
         o1, o2 = torch.empty_like(x), torch.empty_like(x)
-        if op == "add_rmsnorm":
+        if op.startswith("add_rmsnorm"):
             return lambda: ops.add_rmsnorm(x, r, w, out_res=o1, out=o2)
-        if op == "rmsnorm":
+        if op.startswith("rmsnorm"):
             return lambda: ops.rmsnorm(x, w, out=o1)
         return lambda: ops.add(x, r, out=o1)
     if op in ("gated", "gated_model"):
