@@ -290,6 +290,28 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> dict | None:
     clocks = sampler.stop() if sampler else None
     assert int(cp.buf.err_flag.item()) == 0
 
+    # Optional: gather every rank's output rows (NCCL over NVLink).  Not part of the metric: the path itself has no
+    # exchange step; this only says what assembling the full [global tokens, 3136] tensor on every GPU would add.
+    allgather = None
+    if args.allgather and world > 1:
+        import torch.distributed as dist
+        full = torch.empty(world * T, 3136, dtype=torch.bfloat16, device=f"cuda:{local_rank}")
+        for _ in range(3):
+            dist.all_gather_into_tensor(full, cp.buf.normed)
+        torch.cuda.synchronize()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(args.steps):
+            dist.all_gather_into_tensor(full, cp.buf.normed)
+        g1.record()
+        torch.cuda.synchronize()
+        ag_ms = max_over_ranks(g0.elapsed_time(g1)) / args.steps
+        recv = (world - 1) * T * 3136 * 2
+        allgather = {"ms": round(ag_ms, 4), "bytes_received_per_gpu": recv, "gbs_per_gpu": round(recv / ag_ms / 1e6, 1),
+                     "backend": "nccl all_gather_into_tensor", "note": "timed separately; not included in value or e2e"}
+        del full
+
     # end to end through the host-buffer call
     ids_host = cp.buf.ids.cpu().pin_memory()
     cp.run_from_host(ids_host)
@@ -345,6 +367,8 @@ def run_b200(args, rank: int, world: int, local_rank: int) -> dict | None:
         "gpu_launches": int(launches),
         "clocks": clocks,
     }
+    if allgather:
+        out["allgather"] = allgather
     if world == 1:
         # BASELINE.json configs[1..3] (and the gather) at their own sizes, each op alone: batches of 10 back-to-back
         # launches over rotating buffer sets larger than L2, CUDA events, median of 10 batches.
@@ -451,6 +475,7 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=TOKENS_PER_GPU, help="tokens per GPU (weak scaling)")
     ap.add_argument("--cpu-tokens", type=int, default=2048, help="token sample of the CPU legs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--allgather", action="store_true", help="also time an NCCL all-gather of the output rows (N > 1), reported separately")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
