@@ -245,6 +245,8 @@ rmsnorm_f32_kernel(const float* __restrict__ x, float* y, const float* __restric
 
 int launch_norm_cluster(bool fuse, const void* x, const void* r, const float* w, void* out_res, void* out,
                         int64_t rows, int64_t cols, float eps, int cluster, cudaStream_t st);   // rmsnorm_cluster.cu
+int launch_norm_staged_single(bool fuse, const void* x, const void* r, const float* w, void* out_res, void* out,
+                              int64_t rows, int64_t cols, float eps, cudaStream_t st);           // rmsnorm_cluster.cu
 int launch_norm_tma(bool fuse, const void* x, const void* r, const float* w, void* out_res, void* out,
                     int64_t rows, int64_t cols, float eps, cudaStream_t st);   // rmsnorm_tma.cu
 
@@ -267,6 +269,10 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
     const int cluster = tune("norm.cluster", 0);
     if (cluster >= 2 || (cluster == 0 && nv > 8 * 512)) {
         const int s = launch_norm_cluster(FUSE_ADD, x, r, w, out_res, out, rows, cols, eps, cluster, st);
+        if (s != NMT_ERR_UNSUPPORTED) return s;
+    }
+    if (!FUSE_ADD && cluster == 0 && nv > 2560 && nv <= 8 * 512 && tune("norm.staged_single", 1) == 1) {
+        const int s = launch_norm_staged_single(false, x, r, w, out_res, out, rows, cols, eps, st);
         if (s != NMT_ERR_UNSUPPORTED) return s;
     }
     if (tune("norm.variant", kDefaultNormVariant) == 3 && nv <= 8 * 512) {

@@ -320,13 +320,14 @@ static int launch_staged(const void* x, const void* r, const float* w, void* out
 }
 
 // Staged form if some cluster size gives at least two stages within the shared-memory budget; else NMT_ERR_UNSUPPORTED.
+// cluster = 0: smallest of 2 / 4 / 8 that fits; 1: a single CTA per row (the ring without the exchange partners).
 static int launch_norm_cluster_staged(bool fuse, const void* x, const void* r, const float* w, void* out_res, void* out,
                                       int64_t rows, int nv, float inv_cols, float eps, int cluster, cudaStream_t st) {
     // The smallest cluster whose share gives a ring of at least two stages: measured, a smaller cluster with a
     // shallower ring beats a larger one with a deeper ring every time (e.g. 476 vs 507 us at 8192 x 40,000 fused).
     int best_c = 0, best_stages = 0;
-    for (int c = 2; c <= kClusterMax && best_c == 0; c *= 2) {
-        if (cluster >= 2 && c != cluster) continue;
+    for (int c = (cluster == 1 ? 1 : 2); c <= kClusterMax && best_c == 0; c *= 2) {
+        if (cluster >= 1 && c != cluster) continue;
         const int pc = (nv + c - 1) / c;
         if ((pc + kStagedBlock - 1) / kStagedBlock > 8) continue;     // a thread keeps its columns' weights in registers
         const size_t stage = (size_t)pc * 16 * (fuse ? 2 : 1);
@@ -350,6 +351,16 @@ static int launch_norm_cluster_staged(bool fuse, const void* x, const void* r, c
     if (slots <= 6) NMT_STAGED_CASE(6);
     NMT_STAGED_CASE(8);
 #undef NMT_STAGED_CASE
+}
+
+// One CTA per row with the row staged in shared memory: for rows that fit one CTA's registers only at 6 - 8 vectors
+// per thread (20,480 - 32,768 columns), where the register kernel has too few bytes in flight
+// (plain norm at 32,768 columns: 6.2 vs 4.7 TB/s; with the residual add the register kernel stays ahead).
+int launch_norm_staged_single(bool fuse, const void* x, const void* r, const float* w, void* out_res, void* out,
+                              int64_t rows, int64_t cols, float eps, cudaStream_t st) {
+    const int64_t nv = cols / 8;
+    if (nv > 8 * kStagedBlock) return NMT_ERR_UNSUPPORTED;
+    return launch_norm_cluster_staged(fuse, x, r, w, out_res, out, rows, static_cast<int>(nv), 1.0f / static_cast<float>(cols), eps, 1, st);
 }
 
 // Returns NMT_ERR_UNSUPPORTED when the row does not fit a cluster of 8 (more than 262,144 bf16) or `cluster`

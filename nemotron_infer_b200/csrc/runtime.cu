@@ -27,6 +27,7 @@ static Knob g_knobs[] = {
     {"norm.cluster", {0}},        // RMSNorm: 0 = cluster of CTAs per row only for rows one CTA cannot hold, 2/4/8 = always, 1 = never
     {"norm.cluster_staged", {0}}, // cluster RMSNorm: 1 (default) = row shares staged in shared memory by bulk copies, 2 = registers only
     {"norm.cluster_stages", {0}}, // cluster RMSNorm (staged): ring depth, 2..4 (default: what fits 200 KB)
+    {"norm.staged_single", {0}},  // plain RMSNorm, 20,480 - 32,768 columns: 1 (default) = row staged in shared memory, 2 = register kernel
     {"norm.cluster_block", {0}},  // cluster RMSNorm: threads per CTA, 512 (default) or 256
     {"norm.cluster_ctas_per_sm", {0}},  // cluster RMSNorm: CTAs per SM the grid is sized for (default 3)
     {"norm.variant", {0}},        // 0 = default (3), 1 = warp-per-row registers, 2 = TMA-staged tiles, 3 = CTA-per-row registers

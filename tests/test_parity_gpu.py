@@ -62,7 +62,7 @@ def test_norm_golden_fixture(ops):
     assert_ulp(ops.rmsnorm(dev(x), dev(w)), bf16_from_bits(d["cfg1_plain_out"]), "fixture rmsnorm")
 
 
-@pytest.mark.parametrize("cols", [8, 64, 256, 520, 1024, 2048, 3136, 4096, 4104, 12544, 40000])
+@pytest.mark.parametrize("cols", [8, 64, 256, 520, 1024, 2048, 3136, 4096, 4104, 12544, 20488, 24576, 32768, 40000])
 @pytest.mark.parametrize("rows", [1, 3, 37])
 def test_norm_shapes(ops, rows, cols):
     g = torch.Generator().manual_seed(rows * 100003 + cols)
