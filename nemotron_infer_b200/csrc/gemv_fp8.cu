@@ -3,6 +3,10 @@
 // With one token the projection is pure weight streaming (24-55 MB of e4m3 per matrix, 5.4 GB per token for the
 // whole model, ops/gemv.cuh:4-6): the only thing that matters is how fast W crosses HBM, and a matrix is gone in
 // a few microseconds, so every SM has to have deep loads in flight from its first cycle.
+//
+// Three kernels live here.  The default (gemv_w8a16_mma_kernel, further down) runs the inner product on
+// mma.sync and needs K % 64 == 0; the two CUDA-core kernels that come first are the general fallback (any K that
+// is a multiple of 16) and keep exact fp32 products for every x ("gemv.variant" = 1 / 2).  Common to all:
 //   * Persistent grid, one CTA of 8 warps per SM slot.  x is converted to fp32 once per CTA into shared memory
 //     (16 floats per 16 weights come back as four LDS.128, no per-use unpacking).
 //   * A work unit is (row, K-slice): rows are cut into SPLIT slices of ~3 KB so that short-and-wide matrices
