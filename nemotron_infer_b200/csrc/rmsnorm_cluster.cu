@@ -101,12 +101,12 @@ rmsnorm_cluster_kernel(const uint4* x, const uint4* r, const float* __restrict__
 // (plain) to 128 KB (fused) in flight, which is what holds it at 4 - 6 TB/s.  Here every CTA owns a ring of
 // STAGES row shares in shared memory.  A row share is one contiguous 16-byte-aligned range of the row, so one
 // elected thread moves it with ONE bulk copy per input that completes on an mbarrier; up to ~190 KB per SM are
-// in flight while the 512 threads work on the share that has landed: they pull it into registers (at most 8
-// vectors each), hand the stage straight back to the producer, reduce, exchange the partial sums with the other
-// CTAs of the cluster by st.async (a store into a peer's shared memory that counts bytes on an mbarrier there)
-// and scale from registers.  No cluster barrier inside the loop; every wait is a bounded poll of an mbarrier in
-// this CTA's own shared memory.  A row is done in two halves - sum of squares and send, then receive and scale -
-// and row i+1's first half runs before row i's second, so the exchange is off the critical path.  That lets a CTA
+// in flight while the 512 threads work on the shares that have landed: they reduce a share where it lies,
+// exchange the partial sums with the other CTAs of the cluster by st.async (a store into a peer's shared memory
+// that counts bytes on an mbarrier there), scale the share out of the stage and only then hand the stage back to
+// the producer.  No cluster barrier inside the loop; every wait is a bounded poll of an mbarrier in this CTA's
+// own shared memory.  A row is done in two halves - sum of squares and send, then receive and scale - and row
+// i+1's first half runs before row i's second, so the exchange is off the critical path.  That lets a CTA
 // send row i+1 while a peer still sits before its second half of row i-2 (this CTA needed only the peer's row i-1
 // partial sum to get here), hence four partial-sum slots and barriers, indexed by row % 4.
 // ---------------------------------------------------------------------------------------------
@@ -114,7 +114,7 @@ NMT_DEFINE_TIMEOUT_READER();
 
 constexpr int kStagedBlock = 512;
 constexpr int kStagedMaxStages = 4;
-constexpr int kPartSlots = 4;          // partial-sum slots: rows i-2 .. i+1 can be in use at the same time (see below)
+constexpr int kPartSlots = 4;          // partial-sum slots: rows i-2 .. i+1 can be in use at the same time (see above)
 constexpr size_t kStagedSmemBudget = 200 * 1024;
 
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, int rank) {
