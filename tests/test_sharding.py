@@ -63,3 +63,32 @@ def test_two_rank_timing_reduction_and_row_count():
         assert p.exitcode == 0
     assert [g[1] for g in got] == [15.0, 15.0]      # max over ranks, seen by every rank
     assert [g[2] for g in got] == [1001, 1001]      # shards cover every row exactly once
+
+
+def _gather_main(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    # the optional output all-gather of bench.py: equal shards, concatenated in rank order = the unsharded tensor
+    total, hidden = 64, 16
+    full = torch.arange(total * hidden, dtype=torch.float32).reshape(total, hidden)
+    lo, hi = chain.shard_range(total, rank, world)
+    mine = full[lo:hi].contiguous()
+    out = torch.empty(total, hidden)
+    dist.all_gather_into_tensor(out, mine)
+    q.put((rank, bool(torch.equal(out, full))))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_output_gather_restores_row_order():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_gather_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == [(0, True), (1, True)]
