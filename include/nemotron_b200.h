@@ -22,6 +22,11 @@
  *   - rows == 0 / n == 0 is a successful no-op.
  *   - Norm weights are fp32 (model/mlp_block.cuh:76), eps goes inside the rsqrt
  *     after the mean (ops/reduce.cuh:174,438).
+ *   - The fp32 vectors of the bf16 entry points (norm weights, conv taps and
+ *     bias) are read with 16-byte loads and must be 16-byte aligned; only the
+ *     all-fp32 twins (nmt_*_f32) accept 4-byte alignment.  The reference's
+ *     BumpAllocator and torch both hand out at least 128-byte alignment
+ *     (tensor/allocator.cuh:61,80), so its call sites satisfy this.
  */
 #ifndef NEMOTRON_B200_H
 #define NEMOTRON_B200_H
@@ -171,7 +176,13 @@ int nmt_causal_conv1d_silu_f32(const float* x, const float* w, const float* bias
  * nemotron::ops::gemv_fp8 (ops/gemv.cuh:87-104; kernel :48-85), same arguments: W is [N, K] row-major e4m3 with
  * one fp32 scale per output row, x is K bf16 activations (not quantised).  K % 16 == 0, W 16-byte aligned.
  * When K % 64 == 0 the products run on tensor cores with x held as f16 times a power of two taken from max|x|:
- * exact for elements within 2^-28 of the maximum (nmt_tune_set("gemv.variant", 1) keeps fp32 products). */
+ * exact for elements within 2^-28 of the maximum (nmt_tune_set("gemv.variant", 1) keeps fp32 products).
+ * Ordering contract: W and w_scale are model constants to this kernel -- its first weight loads are issued
+ * before it waits for the kernel that precedes it on the stream (programmatic dependent launch), so that
+ * preceding kernel must not be the one that writes W or w_scale (an on-the-fly weight quantiser, a staging
+ * copy kernel).  Put any other kernel, an event or a stream synchronisation between such a producer and this
+ * call, or switch the overlap off with nmt_tune_set("launch.pdl", 2).  x, the norm weight and the residual have
+ * no such restriction: they are read after the wait. */
 int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale, void* y_bf16, int64_t N, int64_t K,
                    void* stream);
 
@@ -244,7 +255,8 @@ int nmt_rmsnorm_gated_quant_fp8(const void* y, const void* z, const float* w, vo
  *     array is 256 + 4 * NMT_STATIC_SCRATCH_MAX_ROWS bytes and is resident on every GPU that loads the library
  *     for the life of the process.
  *   - The first call on each device looks up the array's device address (with that device current) and caches
- *     it; make that first call outside any stream capture.
+ *     it; make that first call outside any stream capture.  The cached address stays valid until that device
+ *     is reset (cudaDeviceReset); a process that resets a device must not call this entry point on it again.
  *   - All calls on a device share the one array.  Calls are safe back to back on one stream (each call resets
  *     what it needs); two calls whose kernels can overlap on the GPU (different streams, no ordering between
  *     them) race on the array and give wrong results -- order them, or use the workspace form for one. */

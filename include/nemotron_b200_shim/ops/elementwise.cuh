@@ -11,6 +11,7 @@
 #include <cstddef>
 
 #include "../../nemotron_b200.h"
+#include "nmt_shim_check.h"
 
 namespace nemotron::ops {
 
@@ -32,8 +33,8 @@ inline void elementwise_ops_fp32(float* in0, float* in1, float* out0, const size
     static_assert(ops_type == kElementwiseAdd || ops_type == kElementwiseRelu2,
                   "nemotron_b200 provides only the operators on the model's path: Add and Relu2");
     (void)scale; (void)bias; (void)clamp_min; (void)clamp_max;
-    if (ops_type == kElementwiseAdd) nmt_add_f32(in0, in1, out0, static_cast<int64_t>(size), stream);
-    else nmt_relu2_f32(in0, out0, static_cast<int64_t>(size), stream);
+    if (ops_type == kElementwiseAdd) detail::nmt_shim_check(nmt_add_f32(in0, in1, out0, static_cast<int64_t>(size), stream), "nmt_add_f32");
+    else detail::nmt_shim_check(nmt_relu2_f32(in0, out0, static_cast<int64_t>(size), stream), "nmt_relu2_f32");
 }
 
 template <ElementwiseType ops_type>
@@ -44,8 +45,8 @@ inline void elementwise_ops_bf16(const __nv_bfloat16* in0, const __nv_bfloat16* 
     static_assert(ops_type == kElementwiseAdd || ops_type == kElementwiseRelu2,
                   "nemotron_b200 provides only the operators on the model's path: Add and Relu2");
     (void)scale; (void)bias; (void)clamp_min; (void)clamp_max;
-    if (ops_type == kElementwiseAdd) nmt_add_bf16(in0, in1, out0, static_cast<int64_t>(size), stream);
-    else nmt_relu2_bf16(in0, out0, static_cast<int64_t>(size), stream);
+    if (ops_type == kElementwiseAdd) detail::nmt_shim_check(nmt_add_bf16(in0, in1, out0, static_cast<int64_t>(size), stream), "nmt_add_bf16");
+    else detail::nmt_shim_check(nmt_relu2_bf16(in0, out0, static_cast<int64_t>(size), stream), "nmt_relu2_bf16");
 }
 
 }  // namespace nemotron::ops

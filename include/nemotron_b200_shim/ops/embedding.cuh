@@ -10,6 +10,7 @@
 #include <cstdint>
 
 #include "../../nemotron_b200.h"
+#include "nmt_shim_check.h"
 
 namespace nemotron::ops {
 
@@ -17,7 +18,7 @@ template <int Hidden>
 inline void embedding_lookup(const __nv_bfloat16* table, const int64_t* token_ids, __nv_bfloat16* out,
                              const size_t num_tokens, cudaStream_t stream = nullptr) {
     static_assert(Hidden % 8 == 0, "rows are copied in 16-byte units");
-    nmt_embedding_bf16_i64(table, token_ids, out, static_cast<int64_t>(num_tokens), Hidden, 0, nullptr, stream);
+    detail::nmt_shim_check(nmt_embedding_bf16_i64(table, token_ids, out, static_cast<int64_t>(num_tokens), Hidden, 0, nullptr, stream), "nmt_embedding_bf16_i64");
 }
 
 }  // namespace nemotron::ops

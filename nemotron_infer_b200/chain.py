@@ -49,6 +49,58 @@ def bytes_per_token(ids_bytes: int = 4) -> int:
     return gather + 42 * (4 * HIDDEN * 2) + 21 * (3 * D_INNER * 2) + 17 * (2 * INTER * 2)
 
 
+BATCH_BLOCK_ROWS = 2048   # granularity of the seeded generation of a global batch (see batch_shard)
+
+
+def batch_shard(global_tokens: int, lo: int, hi: int, device, seed: int = 0, vocab: int = VOCAB,
+                ids_dtype=torch.int32, mixer_sets: int = 2) -> dict:
+    """Rows [lo, hi) of ONE seeded global batch of `global_tokens` tokens, as the `init` of a ChainPass.
+
+    The batch is defined block by block: rows [k*BATCH_BLOCK_ROWS, (k+1)*BATCH_BLOCK_ROWS) of every
+    per-token tensor come from a generator seeded with (seed, tensor, k), so the values of a row do not
+    depend on which rank generates it or on how many ranks there are; a rank generates only the blocks
+    its rows touch.  The table and the norm weights (replicated on every GPU) have seeds of their own.
+    Value distributions are the benchmark configuration's: table 0.02*N(0,1), ids uniform over the
+    vocabulary, mixer outputs / y / z N(0,1), u 2*N(0,1), weights 1 + 0.1*N(0,1); generated in fp32 and
+    cast to bf16."""
+    if not (0 <= lo <= hi <= global_tokens):
+        raise ValueError("bad row range")
+    dev, bf = torch.device(device), torch.bfloat16
+
+    def gen(tag: int, block: int = 0) -> torch.Generator:
+        g = torch.Generator(device=dev)
+        g.manual_seed((int(seed) * 1000003 + tag) * 1000003 + block)
+        return g
+
+    def rows(tag: int, cols: int, scale: float = 1.0) -> torch.Tensor:
+        out = torch.empty(hi - lo, cols, device=dev, dtype=bf)
+        for k in range(lo // BATCH_BLOCK_ROWS, -(-hi // BATCH_BLOCK_ROWS) if hi > lo else 0):
+            b0 = k * BATCH_BLOCK_ROWS
+            n = min(BATCH_BLOCK_ROWS, global_tokens - b0)
+            blk = (scale * torch.randn(n, cols, generator=gen(tag, k), device=dev, dtype=torch.float32)).to(bf)
+            s0, s1 = max(lo, b0), min(hi, b0 + n)
+            out[s0 - lo:s1 - lo] = blk[s0 - b0:s1 - b0]
+        return out
+
+    ids = torch.empty(hi - lo, device=dev, dtype=torch.int64)
+    for k in range(lo // BATCH_BLOCK_ROWS, -(-hi // BATCH_BLOCK_ROWS) if hi > lo else 0):
+        b0 = k * BATCH_BLOCK_ROWS
+        n = min(BATCH_BLOCK_ROWS, global_tokens - b0)
+        blk = torch.randint(0, vocab, (n,), generator=gen(1, k), device=dev, dtype=torch.int64)
+        s0, s1 = max(lo, b0), min(hi, b0 + n)
+        ids[s0 - lo:s1 - lo] = blk[s0 - b0:s1 - b0]
+    table = torch.empty(vocab, HIDDEN, device=dev, dtype=bf)
+    g_t, step = gen(0), 8192
+    for r0 in range(0, vocab, step):                 # chunked: keeps the fp32 temporary small
+        table[r0:r0 + step] = (0.02 * torch.randn(min(step, vocab - r0), HIDDEN, generator=g_t, device=dev,
+                                                  dtype=torch.float32)).to(bf)
+    g_w = gen(2)
+    norm_w = 1.0 + 0.1 * torch.randn(N_LAYERS, HIDDEN, generator=g_w, device=dev, dtype=torch.float32)
+    gated_w = 1.0 + 0.1 * torch.randn(21, D_INNER, generator=g_w, device=dev, dtype=torch.float32)
+    return dict(table=table, ids=ids.to(ids_dtype), mixer_out=[rows(10 + j, HIDDEN) for j in range(mixer_sets)],
+                y=rows(3, D_INNER), z=rows(4, D_INNER), u=rows(5, INTER, 2.0), norm_w=norm_w, gated_w=gated_w)
+
+
 @dataclass
 class ChainBuffers:
     table: torch.Tensor
@@ -106,6 +158,8 @@ class ChainPass:
         self.launches_per_pass = 1 + 42 + 21 + 17
         self._host_ids = None
         self._host_out = None
+        self.graph = None
+        self.graph_launches = 0
 
     def run(self) -> torch.Tensor:
         """Enqueues one pass on torch's current stream; returns the final normed hidden states [T, HIDDEN]."""
@@ -130,23 +184,31 @@ class ChainPass:
         self.run()                                   # warm-up outside the capture (one-time kernel attributes)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count()
         with torch.cuda.graph(graph):
             self.run()
         self.graph = graph
+        self.graph_launches = ops.launch_count() - before   # kernel nodes one replay enqueues
 
     def replay(self) -> torch.Tensor:
         """Replays the captured pass on the current stream; same buffers, same result as run()."""
         self.graph.replay()
         return self.buf.normed
 
-    def run_from_host(self, ids_host: torch.Tensor) -> torch.Tensor:
+    def run_from_host(self, ids_host: torch.Tensor, full_output: torch.Tensor | None = None) -> torch.Tensor:
         """The end-to-end call: token ids arrive in (pinned) host memory, the last token's normed hidden
-        state comes back to host memory — what the engine's prefill hands to lm_head (engine.py:241-251)."""
+        state comes back to host memory — what the engine's prefill hands to lm_head (engine.py:241-251).
+        The pass is the captured graph when capture() has been called, host-launched otherwise.  With
+        `full_output` (a pinned [T, HIDDEN] bf16 host tensor) every normed row is copied back instead."""
         b = self.buf
         if self._host_out is None:
             self._host_out = torch.empty(HIDDEN, dtype=torch.bfloat16).pin_memory()
         b.ids.copy_(ids_host, non_blocking=True)
-        normed = self.run()
+        normed = self.replay() if getattr(self, "graph", None) is not None else self.run()
+        if full_output is not None:
+            full_output.copy_(normed, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+            return full_output
         self._host_out.copy_(normed[self.tokens - 1], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self._host_out

@@ -40,6 +40,7 @@ embedding_relay_kernel(const uint8_t* __restrict__ table, const IdT* __restrict_
     const int64_t my_chunks = my_blocks * kIdBlock;
     bool alive = true;
     int64_t my_id = 0;
+    int64_t filled = 0, stored = 0;     // chunks whose slot fill was started / whose row was handed to a bulk store
 
     for (int64_t i = 0; i < my_chunks + LAG && alive; ++i) {
         if (i < my_chunks) {
@@ -71,6 +72,7 @@ embedding_relay_kernel(const uint8_t* __restrict__ table, const IdT* __restrict_
                         mbar_arrive(full + s);
                     }
                 }
+                filled = i + 1;
             }
         }
         const int64_t j = i - LAG;
@@ -83,11 +85,19 @@ embedding_relay_kernel(const uint8_t* __restrict__ table, const IdT* __restrict_
                     if (alive) {
                         bulk_store(out + (size_t)tok * row_bytes, ring + (size_t)s * slot_stride, row_bytes);
                         bulk_commit();
+                        stored = j + 1;
                     }
                 }
                 alive = __shfl_sync(0xffffffffu, alive, 0);
             }
         }
+    }
+    // A wait ran out (counted; the results are void): bulk loads into this relay's slots may still be in flight.
+    // Wait, bounded again, for every slot that was filled and never stored, so that no copy lands in shared
+    // memory after the CTA has left.
+    if (!alive && lane == 0) {
+        for (int64_t c = stored; c < filled; ++c)
+            mbar_wait(full + static_cast<int>(c % STAGES), static_cast<uint32_t>(c / STAGES) & 1u);
     }
     // Shared memory must outlive every bulk store that reads it.
     if (lane == 0) bulk_wait_all<0>();

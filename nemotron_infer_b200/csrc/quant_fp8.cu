@@ -122,7 +122,8 @@ quant_kernel(const uint4* x, uint2* out, const unsigned int* amax_word, float* s
 template <int SLOTS, bool FUSE_ADD>
 __global__ void __launch_bounds__(512)
 norm_stats_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, uint4* out_res,
-                  float* rstd_out, unsigned int* amax_word, int64_t rows, int nv, float inv_cols, float eps) {
+                  float* rstd_out, unsigned int* amax_word, int64_t rows, int nv, float inv_cols, float eps,
+                  bool butterfly) {
     pdl_wait();
     __shared__ __align__(16) float s_part[2][16];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -158,8 +159,12 @@ norm_stats_kernel(const uint4* x, const uint4* r, const float* __restrict__ w, u
         const float ss = warp_sum(acc.x + acc.y);
         if (lane == 0) s_part[flip][wid] = ss;
         __syncthreads();
+        // The warps' partial sums are added in the order of the kernel nmt_rmsnorm_bf16 runs at this width, so that
+        // rstd (and with it every output byte) equals the unfused norm's: sequentially for the register kernel, as a
+        // butterfly for the shared-memory-staged kernel that takes plain norms of 20,488 - 32,768 columns.
         float total = 0.f;
-        for (int i = 0; i < nwarps; ++i) total += s_part[flip][i];
+        if (butterfly) total = warp_sum(lane < nwarps ? s_part[flip][lane] : 0.f);
+        else for (int i = 0; i < nwarps; ++i) total += s_part[flip][i];
         const float rstd = rsqrtf(total * inv_cols + eps);
         if (threadIdx.x == 0) rstd_out[row] = rstd;
         const float2 rs = make_float2(rstd, rstd);
@@ -229,60 +234,6 @@ norm_quant_kernel(const uint4* h, const float* __restrict__ w, const float* __re
     pdl_trigger();
 }
 
-// The same pass on 32-byte accesses: a thread takes two adjacent vectors with one 256-bit load and writes their
-// sixteen e4m3 bytes with one 16-byte store.  Optional: it did not beat the 16-byte layout consistently.
-// Needs an even number of vectors per row, a 32-byte aligned source and a 16-byte aligned destination.
-__device__ __forceinline__ void ld_stream256(const uint4* p, uint4& lo, uint4& hi) {
-    asm volatile("ld.global.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w) : "l"(p));
-}
-
-template <int SLOTS, int ROWS>
-__global__ void __launch_bounds__(256)
-norm_quant_wide_kernel(const uint4* h, const float* __restrict__ w, const float* __restrict__ rstd_in,
-                       const unsigned int* amax_word, uint4* out, float* scale_out, int64_t rows, int npairs) {
-    pdl_wait();
-    const float s = scale_from_amax(__uint_as_float(*amax_word));
-    const float inv = 1.f / s;
-    if (blockIdx.x == 0 && threadIdx.x == 0 && scale_out) *scale_out = s;
-#pragma unroll 1
-    for (int64_t row0 = (int64_t)blockIdx.x * ROWS; row0 < rows; row0 += (int64_t)gridDim.x * ROWS) {
-        uint4 lo[ROWS][SLOTS], hi[ROWS][SLOTS];
-        float rstd[ROWS];
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            const int64_t row = row0 + r;
-            rstd[r] = row < rows ? __ldg(rstd_in + row) : 0.f;
-#pragma unroll
-            for (int q = 0; q < SLOTS; ++q) {
-                const int p = q * blockDim.x + threadIdx.x;
-                if (row < rows && p < npairs) ld_stream256(h + (row * npairs + p) * 2, lo[r][q], hi[r][q]);
-            }
-        }
-#pragma unroll
-        for (int q = 0; q < SLOTS; ++q) {
-            const int p = q * blockDim.x + threadIdx.x;
-            if (p < npairs) {
-                const float* wp = w + p * 16;
-                const float4 w0 = ld_weight4(wp), w1 = ld_weight4(wp + 4), w2 = ld_weight4(wp + 8), w3 = ld_weight4(wp + 12);
-#pragma unroll
-                for (int r = 0; r < ROWS; ++r) {
-                    const int64_t row = row0 + r;
-                    if (row < rows) {
-                        float2 pa[4], pb[4];
-                        unpack8x2(lo[r][q], pa);
-                        unpack8x2(hi[r][q], pb);
-                        const uint2 qa = quant8(scale8(pa, rstd[r], w0, w1), inv);
-                        const uint2 qb = quant8(scale8(pb, rstd[r], w2, w3), inv);
-                        st_stream(out + row * npairs + p, make_uint4(qa.x, qa.y, qb.x, qb.y));
-                    }
-                }
-            }
-        }
-    }
-    pdl_trigger();
-}
-
 static int ew_grid(int64_t nv, int block, int unroll) {
     return grid_for(nv, block * unroll, kSmCount * 32);
 }
@@ -323,21 +274,17 @@ static int launch_norm_quant(const void* x, const void* r, const float* w, void*
     const int slots = static_cast<int>((nv + block - 1) / block);
     const int grid = grid_for(rows, 1, 0x7fffffff);
     const int qrows = tune("quant.rows_per_cta", 2);
+    const bool butterfly = !FUSE_ADD && nv > 2560 && tune("norm.cluster", 0) == 0 && tune("norm.staged_single", 1) == 1;
     const float inv_cols = 1.0f / static_cast<float>(cols);
     auto X = static_cast<const uint4*>(x);
     auto R = static_cast<const uint4*>(r);
     auto OR = static_cast<uint4*>(out_res);
     const uint4* H = FUSE_ADD ? static_cast<const uint4*>(out_res) : X;
     auto Q = static_cast<uint2*>(out_fp8);
-    // pass 2 on 32-byte accesses when asked for and the layout allows it (knob quant.wide = 1).  Measured: +2 % at
-    // 65,536 tokens with four rows per CTA, -8 % at 8192 tokens, so the 16-byte layout stays the default.
-    const bool wide = tune("quant.wide", 2) == 1 && (nv % 2) == 0 && nv / 2 <= 2 * 256 &&
-                      (reinterpret_cast<uintptr_t>(H) & 31u) == 0 && aligned16(out_fp8);
 #define NMT_NQ_CASE(S)                                                                                          \
     do {                                                                                                        \
         launch_kernel(norm_stats_kernel<S, FUSE_ADD>, grid, block, 0, st, X, R, w, OR, rstd, amax_word, rows,   \
-                      (int)nv, inv_cols, eps);                                                                  \
-        if (wide) break;                                                                                        \
+                      (int)nv, inv_cols, eps, butterfly);                                                                \
         if (qrows >= 4) launch_kernel(norm_quant_kernel<S, 4>, grid_for(rows, 4, 0x7fffffff), block, 0, st, H, w, static_cast<const float*>(rstd), \
                       static_cast<const unsigned int*>(amax_word), Q, scale_out, rows, (int)nv);                \
         else if (qrows >= 2) launch_kernel(norm_quant_kernel<S, 2>, grid_for(rows, 2, 0x7fffffff), block, 0, st, H, w, static_cast<const float*>(rstd), \
@@ -352,21 +299,6 @@ static int launch_norm_quant(const void* x, const void* r, const float* w, void*
     else if (slots <= 6) NMT_NQ_CASE(6);
     else NMT_NQ_CASE(8);
 #undef NMT_NQ_CASE
-    if (wide) {
-        const int npairs = static_cast<int>(nv / 2);
-        const int wslots = (npairs + 255) / 256;
-        int wblock = (npairs + wslots - 1) / wslots;
-        wblock = (wblock + 31) / 32 * 32;
-        auto Q4 = static_cast<uint4*>(out_fp8);
-        const float* RS = rstd;
-        const unsigned int* AW = amax_word;
-        if (wslots <= 1) {
-            if (qrows >= 4) launch_kernel(norm_quant_wide_kernel<1, 4>, grid_for(rows, 4, 0x7fffffff), wblock, 0, st, H, w, RS, AW, Q4, scale_out, rows, npairs);
-            else launch_kernel(norm_quant_wide_kernel<1, 2>, grid_for(rows, 2, 0x7fffffff), wblock, 0, st, H, w, RS, AW, Q4, scale_out, rows, npairs);
-        } else {
-            launch_kernel(norm_quant_wide_kernel<2, 2>, grid_for(rows, 2, 0x7fffffff), wblock, 0, st, H, w, RS, AW, Q4, scale_out, rows, npairs);
-        }
-    }
     return finish_launch(2);
 }
 
@@ -410,6 +342,8 @@ static void* static_scratch_address(int* status) {
 
 int launch_gated_bf16(const void* y, const void* z, const float* w, void* out, int64_t rows, int64_t cols,
                       int64_t group_size, float eps, unsigned int* amax_word, bool* tracked, cudaStream_t st);   // rmsnorm_gated.cu
+int validate_gated_bf16(const void* y, const void* z, const float* w, const void* out, int64_t rows, int64_t cols,
+                        int64_t group_size);                                                                      // rmsnorm_gated.cu
 
 }  // namespace nmt
 
@@ -420,13 +354,14 @@ int nmt_rmsnorm_gated_quant_fp8(const void* y, const void* z, const float* w, vo
                                 int64_t group_size, float eps, void* stream) {
     using namespace nmt;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (rows < 0 || cols <= 0 || (cols % 8) != 0) return NMT_ERR_SHAPE;
-    if (rows == 0) return NMT_OK;
+    // every check first: a rejected call enqueues nothing and leaves the caller's scratch word alone
+    int s = validate_gated_bf16(y, z, w, out_bf16, rows, cols, group_size);
+    if (s != NMT_OK || rows == 0) return s;
     if (!out_fp8 || !amax_scratch) return NMT_ERR_NULL;
     if ((reinterpret_cast<uintptr_t>(out_fp8) & 7u) || !aligned4(amax_scratch) || (scale_out && !aligned4(scale_out))) return NMT_ERR_ALIGN;
     if (cudaMemsetAsync(amax_scratch, 0, sizeof(unsigned int), st) != cudaSuccess) return finish_launch(0);
     bool tracked = false;
-    int s = launch_gated_bf16(y, z, w, out_bf16, rows, cols, group_size, eps, amax_scratch, &tracked, st);
+    s = launch_gated_bf16(y, z, w, out_bf16, rows, cols, group_size, eps, amax_scratch, &tracked, st);
     if (s != NMT_OK) return s;
     const int64_t nv = rows * cols / 8;
     constexpr int U = 4, B = 256;

@@ -1,84 +1,13 @@
 // RMSNorm and fused residual-add + RMSNorm.
 //
-// Register variant: one warp owns one row.  A 3136-wide bf16 row is 392 16-byte
-// vectors, i.e. 13 lane slots (the last one 8 lanes wide).  All loads of a row
-// are issued before the first use, the rounded sum x+r stays in registers
-// between the sum of squares and the scaling, the reduction is five shuffles,
-// and there is no shared memory and no block barrier.  Every activation byte
-// crosses HBM once: read x, read r, write out_res, write out.
+// Default kernel (rows up to 32,768 columns): one CTA per row, the row spread over ~96-160 threads that each hold
+// 3-5 16-byte vectors of x (and r) in registers.  All loads of a row are issued before the first use, the rounded
+// sum x + r stays in registers between the sum of squares and the scaling, the row statistic costs five shuffles
+// plus one block barrier, and every activation byte crosses HBM once: read x, read r, write out_res, write out.
+// Wider rows go to the cluster kernels in rmsnorm_cluster.cu; the two-pass kernel below is the last resort.
 #include "nmt_common.cuh"
 
 namespace nmt {
-
-constexpr int kDefaultNormVariant = 3;   // 1 = warp-per-row registers, 2 = TMA-staged tiles, 3 = CTA-per-row registers
-
-template <int SLOTS, bool FUSE_ADD>
-__global__ void __launch_bounds__(256)
-rmsnorm_rowwarp_kernel(const uint4* x, const uint4* r,
-                       const float* __restrict__ w, uint4* out_res, uint4* out,
-                       int64_t rows, int nv, float inv_cols, float eps) {
-    pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const int warps_per_cta = blockDim.x >> 5;
-    const int64_t warp0 = (int64_t)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
-    const int64_t nwarps = (int64_t)gridDim.x * warps_per_cta;
-#pragma unroll 1
-
-    for (int64_t row = warp0; row < rows; row += nwarps) {
-        const uint4* xr = x + row * nv;
-        const uint4* rr = FUSE_ADD ? r + row * nv : nullptr;
-        uint4 a[SLOTS], b[SLOTS];
-#pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            const int v = s * 32 + lane;
-            if (v < nv) {
-                a[s] = ld_stream(xr + v);
-                if (FUSE_ADD) b[s] = ld_stream(rr + v);
-            } else {
-                a[s] = make_uint4(0, 0, 0, 0);
-                if (FUSE_ADD) b[s] = make_uint4(0, 0, 0, 0);
-            }
-        }
-        float ss = 0.f;
-#pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            float f[8];
-            unpack8(a[s], f);
-            if (FUSE_ADD) {
-                float g[8];
-                unpack8(b[s], g);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) f[k] += g[k];
-                // Round the residual stream to bf16 first: the norm must see what the
-                // next block would read back from memory.
-                a[s] = pack8(f);
-                unpack8(a[s], f);
-                const int v = s * 32 + lane;
-                if (v < nv) st_stream(out_res + row * nv + v, a[s]);
-            }
-#pragma unroll
-            for (int k = 0; k < 8; ++k) ss = fmaf(f[k], f[k], ss);
-        }
-        ss = warp_sum(ss);
-        const float rstd = rsqrtf(ss * inv_cols + eps);
-#pragma unroll
-        for (int s = 0; s < SLOTS; ++s) {
-            const int v = s * 32 + lane;
-            if (v < nv) {
-                float f[8];
-                unpack8(a[s], f);
-                const float4 w0 = ld_weight4(w + v * 8);
-                const float4 w1 = ld_weight4(w + v * 8 + 4);
-                f[0] = (f[0] * rstd) * w0.x; f[1] = (f[1] * rstd) * w0.y;
-                f[2] = (f[2] * rstd) * w0.z; f[3] = (f[3] * rstd) * w0.w;
-                f[4] = (f[4] * rstd) * w1.x; f[5] = (f[5] * rstd) * w1.y;
-                f[6] = (f[6] * rstd) * w1.z; f[7] = (f[7] * rstd) * w1.w;
-                st_stream(out + row * nv + v, pack8(f));
-            }
-        }
-    }
-    pdl_trigger();
-}
 
 // CTA-per-row register variant: blockDim threads share ROWS consecutive rows (thread t owns vectors t,
 // t + blockDim, ... of each), so each thread holds only SLOTS = ceil(vectors / blockDim) vectors of x and r per
@@ -247,8 +176,6 @@ int launch_norm_cluster(bool fuse, const void* x, const void* r, const float* w,
                         int64_t rows, int64_t cols, float eps, int cluster, cudaStream_t st);   // rmsnorm_cluster.cu
 int launch_norm_staged_single(bool fuse, const void* x, const void* r, const float* w, void* out_res, void* out,
                               int64_t rows, int64_t cols, float eps, cudaStream_t st);           // rmsnorm_cluster.cu
-int launch_norm_tma(bool fuse, const void* x, const void* r, const float* w, void* out_res, void* out,
-                    int64_t rows, int64_t cols, float eps, cudaStream_t st);   // rmsnorm_tma.cu
 
 template <bool FUSE_ADD>
 static int launch_norm_bf16(const void* x, const void* r, const float* w, void* out_res, void* out,
@@ -260,10 +187,6 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
     auto OR = static_cast<uint4*>(out_res);
     auto O = static_cast<uint4*>(out);
 
-    if (tune("norm.variant", kDefaultNormVariant) == 2) {
-        const int s = launch_norm_tma(FUSE_ADD, x, r, w, out_res, out, rows, cols, eps, st);
-        if (s != NMT_ERR_UNSUPPORTED) return s;
-    }
     // norm.cluster: 0 = a cluster of CTAs per row where one CTA cannot hold the row in registers (more than 32,768
     // columns), 2 / 4 / 8 = that cluster size for every width, 1 = never (wide rows take the two-pass kernel).
     const int cluster = tune("norm.cluster", 0);
@@ -275,11 +198,12 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
         const int s = launch_norm_staged_single(false, x, r, w, out_res, out, rows, cols, eps, st);
         if (s != NMT_ERR_UNSUPPORTED) return s;
     }
-    if (tune("norm.variant", kDefaultNormVariant) == 3 && nv <= 8 * 512) {
+    if (nv <= 8 * 512) {
         // Default shape: about 160 threads per row (392 vectors -> 3 per thread), at most 8 vectors per thread.
         int block = tune("norm.block", 0);
         if (block <= 0) block = default_norm_block(nv, FUSE_ADD);
         block = block > 512 ? 512 : (block + 31) / 32 * 32;
+        if ((nv + block - 1) / block > 8) block = 512;     // a swept block size too small for this width
         const int slots = static_cast<int>((nv + block - 1) / block);
         const int per_sm = tune("norm.ctas_per_sm", 0);
         const int rows_per_cta = tune("norm.rows_per_cta", 1);
@@ -297,31 +221,13 @@ static int launch_norm_bf16(const void* x, const void* r, const float* w, void* 
         else if (slots <= 4) NMT_CTAROW_CASE(4);
         else if (slots <= 5) NMT_CTAROW_CASE(5);
         else if (slots <= 7) NMT_CTAROW_CASE(7);
-        else if (slots <= 8) NMT_CTAROW_CASE(8);
-        else goto wide;   // more than 8 vectors per thread: fall through to the other variants
+        else NMT_CTAROW_CASE(8);
 #undef NMT_CTAROW_CASE
         return finish_launch(1);
     }
-wide:
-    if (nv > 16 * 32) {
-        const int grid = grid_for(rows, 1, kSmCount * 16);
-        launch_kernel(rmsnorm_rowcta_kernel<FUSE_ADD>, grid, 256, 0, st, X, R, w, OR, O, rows, nv, inv_cols, eps);
-        return finish_launch(1);
-    }
-    int block = tune("norm.block", 64);      // warp-per-row variant
-    block = block > 256 ? 256 : (block + 31) / 32 * 32;
-    const int wpc = block / 32;
-    const int per_sm = tune("norm.ctas_per_sm", 0);
-    const int grid = grid_for(rows, wpc, per_sm > 0 ? kSmCount * per_sm : 0x7fffffff);
-    const int slots = static_cast<int>((nv + 31) / 32);
-#define NMT_NORM_CASE(S)                                                                           \
-    launch_kernel(rmsnorm_rowwarp_kernel<S, FUSE_ADD>, grid, block, 0, st, X, R, w, OR, O, rows, (int)nv, inv_cols, eps)
-    if (slots <= 2) NMT_NORM_CASE(2);
-    else if (slots <= 4) NMT_NORM_CASE(4);
-    else if (slots <= 8) NMT_NORM_CASE(8);
-    else if (slots <= 13) NMT_NORM_CASE(13);
-    else NMT_NORM_CASE(16);
-#undef NMT_NORM_CASE
+    // Wider than one CTA's registers and no cluster launch possible: one CTA per row, two passes.
+    const int grid = grid_for(rows, 1, kSmCount * 16);
+    launch_kernel(rmsnorm_rowcta_kernel<FUSE_ADD>, grid, 256, 0, st, X, R, w, OR, O, rows, nv, inv_cols, eps);
     return finish_launch(1);
 }
 

@@ -161,13 +161,21 @@ static int check_gated(const void* y, const void* z, const float* w, const void*
     return NMT_OK;
 }
 
-int launch_gated_bf16(const void* y, const void* z, const float* w, void* out, int64_t rows, int64_t cols,
-                      int64_t group_size, float eps, unsigned int* amax_word, bool* tracked, cudaStream_t st) {
-    if (tracked) *tracked = false;
+// Every argument check of the bf16 form; NMT_OK means launch_gated_bf16 will launch (or rows == 0).
+int validate_gated_bf16(const void* y, const void* z, const float* w, const void* out, int64_t rows, int64_t cols,
+                        int64_t group_size) {
     int s = check_gated(y, z, w, out, rows, cols, group_size);
     if (s != NMT_OK || rows == 0) return s;
     if ((cols % 8) != 0) return NMT_ERR_SHAPE;
     if (!aligned16(y) || !aligned16(z) || !aligned16(out) || !aligned16(w)) return NMT_ERR_ALIGN;
+    return NMT_OK;
+}
+
+int launch_gated_bf16(const void* y, const void* z, const float* w, void* out, int64_t rows, int64_t cols,
+                      int64_t group_size, float eps, unsigned int* amax_word, bool* tracked, cudaStream_t st) {
+    if (tracked) *tracked = false;
+    int s = validate_gated_bf16(y, z, w, out, rows, cols, group_size);
+    if (s != NMT_OK || rows == 0) return s;
     const int64_t groups = cols / group_size;
     const int64_t items = rows * groups;
 

@@ -30,14 +30,10 @@ static Knob g_knobs[] = {
     {"norm.staged_single", {0}},  // plain RMSNorm, 20,480 - 32,768 columns: 1 (default) = row staged in shared memory, 2 = register kernel
     {"norm.cluster_block", {0}},  // cluster RMSNorm: threads per CTA, 512 (default) or 256
     {"norm.cluster_ctas_per_sm", {0}},  // cluster RMSNorm: CTAs per SM the grid is sized for (default 3)
-    {"norm.variant", {0}},        // 0 = default (3), 1 = warp-per-row registers, 2 = TMA-staged tiles, 3 = CTA-per-row registers
-    {"norm.block", {0}},          // threads per CTA for the warp-per-row kernel
+    {"norm.block", {0}},          // threads per CTA (= per row); 0 = by width
     {"norm.ctas_per_sm", {0}},    // >0: persistent grid of 148*k CTAs; 0: one pass, grid = rows/warps
     {"norm.rows_per_cta", {0}},   // CTA-per-row variant: rows a CTA loads together (1 or 2)
-    {"norm.tma_rows", {0}},       // rows per TMA stage
-    {"norm.tma_stages", {0}},
     {"quant.rows_per_cta", {0}},  // rows a CTA of the norm -> e4m3 pass handles together (1, 2 or 4)
-    {"quant.wide", {0}},          // norm -> e4m3 pass on 256-bit loads / 16-byte stores: 1 = yes, 2 = no (default)
     {"conv.chunk", {0}},          // causal conv1d: time steps per thread (4, 8, 16, 32 or 64)
     {"conv.pairs", {0}},          // causal conv1d: channel pairs per thread (2 = 8-byte vectors, 4 = 16-byte vectors)
     {"conv.unroll", {0}},         // causal conv1d: loads issued ahead of use (4 or 8)
@@ -48,18 +44,13 @@ static Knob g_knobs[] = {
     {"gemv.streams", {0}},        // W8A16 GEMV (mma): k-streams per 16-row tile (1, 2, 4, 8); 0 = by shape
     {"gemv.ctas_per_sm", {0}},    // W8A16 GEMV: persistent CTAs per SM; 0 = by shared-memory footprint
     // gated rmsnorm (bf16)
-    {"gated.variant", {0}},       // 0 = auto, 1 = warp-per-group registers, 2 = TMA-staged rows
     {"gated.block", {0}},
     {"gated.ctas_per_sm", {0}},
     {"gated.rows_per_iter", {0}},
-    {"gated.tma_stages", {0}},
     // relu2 / add (bf16)
-    {"ew.variant", {0}},          // 0 = auto, 1 = register streaming, 2 = TMA-staged chunks
     {"ew.block", {0}},
     {"ew.unroll", {0}},
     {"ew.ctas_per_sm", {0}},
-    {"ew.tma_chunk", {0}},        // bytes per TMA stage
-    {"ew.tma_stages", {0}},
     // embedding gather
     {"emb.variant", {0}},         // 0 = by batch size, 1 = warp-per-row registers, 2 = TMA row relay
     {"emb.block", {0}},
@@ -107,7 +98,7 @@ const char* nmt_status_string(int s) {
     switch (s) {
         case NMT_OK: return "ok";
         case NMT_ERR_NULL: return "null pointer";
-        case NMT_ERR_ALIGN: return "pointer not aligned to the contract (16 bytes for bf16 tensors, 4 for fp32)";
+        case NMT_ERR_ALIGN: return "pointer not aligned to the contract (16 bytes for bf16 tensors and for the fp32 weight / tap / bias vectors of the bf16 entry points, 4 bytes in the fp32 twins)";
         case NMT_ERR_SHAPE: return "bad shape (negative size, cols % 8 != 0, or group size does not divide cols)";
         case NMT_ERR_LAUNCH: return "CUDA launch failed (see nmt_last_cuda_error)";
         case NMT_ERR_UNSUPPORTED: return "unsupported shape or unknown tuning key";

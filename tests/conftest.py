@@ -12,6 +12,19 @@ if ROOT not in sys.path:
 GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 
+# Every 1-ulp comparison of the parity tests records what it observed here; when the environment variable
+# NMT_ULP_REPORT names a file, the list is written there as JSON at the end of the session.
+ULP_LOG: list = []
+
+
+def pytest_sessionfinish(session, exitstatus):
+    path = os.environ.get("NMT_ULP_REPORT")
+    if path and ULP_LOG:
+        import json
+        with open(path, "w") as f:
+            json.dump(ULP_LOG, f, indent=0)
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
 

@@ -75,7 +75,8 @@ def bits(t: torch.Tensor) -> np.ndarray:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--reference", default=os.environ.get("REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference"),
+                    help="the reference checkout (default: $REFERENCE_ROOT, else a directory named 'reference' beside this repository)")
     a = ap.parse_args()
     torch.set_num_threads(1)          # fixed summation order for the fixtures
 

@@ -98,3 +98,33 @@ def test_sharded_chain_equals_unsharded(built_lib):
         part["mixer_out"] = [m[lo:hi] for m in full["mixer_out"]]
         got = chain.ChainPass(hi - lo, "cuda", vocab=vocab, init=part).run()
         assert torch.equal(got.view(torch.int16), ref[lo:hi].view(torch.int16))
+
+
+def test_bench_parity_sample_and_batch_shards(built_lib):
+    """bench.py's own output check (sampled rows of the pass against the oracle) passes on a correct pass and
+    notices a corrupted one; the ranks' shards of one seeded batch give the rows of the whole batch."""
+    import bench
+    from nemotron_infer_b200 import chain
+    G, vocab = 300, 2048
+    whole = chain.ChainPass(G, "cuda", init=chain.batch_shard(G, 0, G, "cuda", seed=8, vocab=vocab))
+    ref = whole.run().clone()
+    rep = bench.parity_sample(whole, 64, seed=1)
+    assert rep["max_ulp"] <= 1 and rep["not_bit_exact"] == [] and rep["err_flag"] == 0 and rep["rows"] >= 32
+    assert sorted(rep["bit_exact"]) == ["act", "final_hidden"]
+    for rank in range(3):
+        lo, hi = chain.shard_range(G, rank, 3)
+        part = chain.ChainPass(hi - lo, "cuda", init=chain.batch_shard(G, lo, hi, "cuda", seed=8, vocab=vocab))
+        assert torch.equal(part.run().view(torch.int16), ref[lo:hi].view(torch.int16))
+    # the captured pass serves the host-buffer call, and a full-output request returns every row
+    whole.capture()
+    ids_host = whole.buf.ids.cpu().pin_memory()
+    rows_host = torch.empty(G, chain.HIDDEN, dtype=torch.bfloat16).pin_memory()
+    last = whole.run_from_host(ids_host).clone()
+    assert torch.equal(last.view(torch.int16), ref[G - 1].cpu().view(torch.int16))
+    assert torch.equal(whole.run_from_host(ids_host, full_output=rows_host).view(torch.int16), ref.cpu().view(torch.int16))
+    assert whole.graph_launches == 81
+    # a wrong byte in the residual stream or the activation is reported
+    whole.final_hidden[0, 0] += 1.0
+    whole.buf.normed[G - 1, 5] = 1000.0
+    bad = bench.parity_sample(whole, 64, seed=1)
+    assert "final_hidden" in bad["not_bit_exact"] and bad["max_ulp"] > 1

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import bf16_from_bits, fptr, golden
+from conftest import ULP_LOG, bf16_from_bits, fptr, golden
 from oracle import torch_golden as og
 
 pytestmark = pytest.mark.gpu
@@ -31,6 +31,7 @@ def dev(t):
 
 def assert_ulp(got, want, what, max_ulp=MAX_ULP, max_frac=MAX_MISMATCH_FRAC):
     rep = og.ulp_report(got, want)
+    ULP_LOG.append(dict(rep, what=what))     # written out at session end when NMT_ULP_REPORT names a file
     assert rep["max_ulp"] <= max_ulp and rep["mismatch_frac"] <= max_frac, f"{what}: {rep}"
     return rep
 
@@ -104,46 +105,22 @@ def test_tuned_launch_shapes_give_the_same_answer(ops):
     x, r, w = og.cfg1_inputs(777)
     want_res, want = og.add_rmsnorm_bf16(x, r, w)
     try:
-        for variant, block, per_sm in ((1, 128, 0), (1, 64, 2), (1, 256, 1), (1, 96, 4), (3, 160, 0), (3, 64, 3)):
-            ops.tune("norm.variant", variant)      # 1 = warp per row, 3 = CTA per row
+        for rows_per_cta, block, per_sm in ((1, 128, 0), (2, 64, 2), (1, 256, 1), (2, 96, 4), (1, 160, 0), (4, 64, 3)):
+            ops.tune("norm.rows_per_cta", rows_per_cta)
             ops.tune("norm.block", block)
             ops.tune("norm.ctas_per_sm", per_sm)
             res, out = ops.add_rmsnorm(dev(x), dev(r), dev(w))
             assert torch.equal(res.cpu(), want_res)
-            assert_ulp(out, want, f"variant={variant} block={block} per_sm={per_sm}")
+            assert_ulp(out, want, f"rows_per_cta={rows_per_cta} block={block} per_sm={per_sm}")
             for cols in (64, 1024, 4096):
                 xs, rs, ws = og.cfg1_inputs(21, cols)
                 wr, wo = og.add_rmsnorm_bf16(xs, rs, ws)
                 res, out = ops.add_rmsnorm(dev(xs), dev(rs), dev(ws))
                 assert torch.equal(res.cpu(), wr)
-                assert_ulp(out, wo, f"variant={variant} cols={cols}", max_frac=0.05)
+                assert_ulp(out, wo, f"rows_per_cta={rows_per_cta} block={block} cols={cols}", max_frac=0.05)
+                assert_ulp(ops.rmsnorm(dev(xs), dev(ws)), og.rmsnorm_bf16(xs, ws), f"plain cols={cols}", max_frac=0.05)
     finally:
-        for k in ("norm.variant", "norm.block", "norm.ctas_per_sm"):
-            ops.tune(k, 0)
-
-
-@pytest.mark.parametrize("rows_per_tile,stages,per_sm", [(4, 4, 1), (8, 2, 1), (2, 3, 2), (1, 8, 3), (3, 2, 1)])
-def test_tma_staged_norm_variant(ops, built_lib, rows_per_tile, stages, per_sm):
-    try:
-        ops.tune("norm.variant", 2)
-        ops.tune("norm.tma_rows", rows_per_tile)
-        ops.tune("norm.tma_stages", stages)
-        ops.tune("norm.ctas_per_sm", per_sm)
-        for T, cols in ((1, 3136), (5, 3136), (2051, 3136), (8192, 3136), (33, 1024), (70, 4096), (9, 64)):
-            g = torch.Generator().manual_seed(T * 31 + cols)
-            x = torch.randn(T, cols, generator=g).to(BF)
-            r = torch.randn(T, cols, generator=g).to(BF)
-            w = og.norm_weight(cols, g)
-            want_res, want = og.add_rmsnorm_bf16(x, r, w)
-            xd = dev(x)
-            out = torch.empty_like(xd)
-            ops.add_rmsnorm(xd, dev(r), dev(w), out_res=xd, out=out)       # in place on the residual stream
-            assert torch.equal(xd.cpu(), want_res), (T, cols)
-            assert_ulp(out, want, f"tma add_rmsnorm {T}x{cols}", max_frac=0.05)
-            assert_ulp(ops.rmsnorm(dev(x), dev(w)), og.rmsnorm_bf16(x, w), f"tma rmsnorm {T}x{cols}", max_frac=0.05)
-        assert built_lib.nmt_device_wait_timeouts() == 0
-    finally:
-        for k in ("norm.variant", "norm.tma_rows", "norm.tma_stages", "norm.ctas_per_sm"):
+        for k in ("norm.rows_per_cta", "norm.block", "norm.ctas_per_sm"):
             ops.tune(k, 0)
 
 
@@ -218,14 +195,43 @@ def test_gated_rows_per_iter_variant_and_in_place(ops):
 
 def test_gated_saturated_gates(ops):
     # very negative gates drive silu to 0, very positive ones to z: neither may produce NaN/Inf
-    y, z, w = og.cfg2_inputs(4)
+    y, z, w = og.cfg2_inputs(6)
     z[0] = -60.0
     z[1] = 60.0
     z[2, ::3] = -20.0
+    # Far below z = -88.7 the golden's fp32 silu is exactly 0 (exp(-z) overflows to inf) and so is the kernel's.
+    z[3] = -100.0
+    z[4, :768] = -100.0
+    z[4, 768:1536:2] = -95.0
+    z[5, 5::7] = -110.0
     want = og.gated_rmsnorm_bf16(y, z, w, 768)
     got = ops.rmsnorm_gated(dev(y), dev(z), dev(w), 768)
     assert torch.isfinite(got.float()).all()
     assert_ulp(got, want, "saturated gates", max_frac=0.05)
+    assert torch.equal(got[3].cpu().float(), torch.zeros(6144)) and torch.equal(want[3].float(), torch.zeros(6144))
+
+
+def test_gated_flush_to_zero_window(ops):
+    """The one documented deviation from the golden: the kernel's silu uses the flush-to-zero SFU forms, so for gates
+    in about (-88.7, -87.3) -- where 1 / (1 + exp(-z)) is an fp32 denormal -- it returns exactly 0 while the golden
+    returns magnitudes of 1e-34 or so (a whole group of such gates; rstd is then rsqrt(eps)).  That is not
+    expressible in ulps; the absolute error is bounded instead.  Mixed into ordinary gates the flushed terms are
+    far below the rounding of the others and the result is within 1 ulp."""
+    y, z, w = og.cfg2_inputs(3)
+    z[0] = -88.0
+    z[1, :768] = -87.6
+    z[2, 1::5] = -88.3
+    want = og.gated_rmsnorm_bf16(y, z, w, 768)
+    got = ops.rmsnorm_gated(dev(y), dev(z), dev(w), 768).cpu()
+    assert torch.isfinite(got.float()).all()
+    assert float(want[0].float().abs().max()) > 0 and float(got[0].float().abs().max()) == 0.0
+    assert float((got[0].float() - want[0].float()).abs().max()) < 1e-30
+    assert float((got[1, :768].float() - want[1, :768].float()).abs().max()) < 1e-30
+    assert_ulp(got[1:2, 768:], want[1:2, 768:], "ordinary groups beside a flushed one")
+    keep = torch.ones(6144, dtype=torch.bool)
+    keep[1::5] = False
+    assert_ulp(got[2][keep], want[2][keep], "ordinary gates mixed with flushed ones", max_frac=0.05)
+    assert float((got[2][~keep].float() - want[2][~keep].float()).abs().max()) < 1e-30
 
 
 def test_gated_fp32_twin(ops, oracle_c):
@@ -396,9 +402,8 @@ def test_embedding_tma_relay_variant(ops, built_lib, stages, warps, per_sm):
 @pytest.mark.parametrize("block", [64, 96, 128, 224, 416, 512])
 def test_cta_per_row_norm_variant(ops, block):
     try:
-        ops.tune("norm.variant", 3)
         ops.tune("norm.block", block)
-        for T, cols in ((1, 3136), (5, 3136), (2051, 3136), (33, 1024), (70, 4096), (9, 64), (3, 12544)):
+        for T, cols in ((1, 3136), (5, 3136), (2051, 3136), (33, 1024), (70, 4096), (9, 64), (3, 12544), (2, 32768)):
             g = torch.Generator().manual_seed(T * 31 + cols)
             x = torch.randn(T, cols, generator=g).to(BF)
             r = torch.randn(T, cols, generator=g).to(BF)
@@ -411,7 +416,6 @@ def test_cta_per_row_norm_variant(ops, block):
             assert_ulp(out, want, f"cta-row add_rmsnorm {T}x{cols}", max_frac=0.05)
             assert_ulp(ops.rmsnorm(dev(x), dev(w)), og.rmsnorm_bf16(x, w), f"cta-row rmsnorm {T}x{cols}", max_frac=0.05)
     finally:
-        ops.tune("norm.variant", 0)
         ops.tune("norm.block", 0)
 
 

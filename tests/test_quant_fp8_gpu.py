@@ -104,12 +104,29 @@ def test_norm_quant_fused_equals_unfused_and_golden(ops, T, cols):
     assert float(s3.item()) == float(s4.item()) and torch.equal(bytes_of(q3), bytes_of(q4))
 
 
-@pytest.mark.parametrize("wide,qrows", [(2, 1), (2, 4), (1, 4), (1, 2)])
-def test_norm_quant_pass_layouts_agree(ops, wide, qrows):
-    """The e4m3 pass has a 16-byte-access and a 32-byte-access layout and 1/2/4 rows per CTA: same bytes from all,
-    including from a source that is only 16-byte aligned (which must fall back to the narrow layout)."""
+@pytest.mark.parametrize("cols", [20480, 20488, 24576, 32768])
+def test_norm_quant_wide_rows_follow_the_unfused_norms_summation_order(ops, cols):
+    """Plain norms of 20,488 - 32,768 columns run in a kernel that adds the warps' partial sums as a butterfly, the
+    narrower ones (and every fused add + norm) sequentially; the quantiser's statistics pass must add in the same
+    order or rstd can differ in its last bit.  Many rows make a last-bit difference show."""
+    T = 512
+    x, r, w = og.cfg1_inputs(T, cols)
+    xd, rd, wd = x.cuda(), r.cuda(), w.cuda()
+    q, s = ops.rmsnorm_quant_fp8(xd, wd)
+    q2, s2 = ops.quantize_fp8(ops.rmsnorm(xd, wd))
+    assert float(s.item()) == float(s2.item()) and torch.equal(bytes_of(q), bytes_of(q2)), "plain norm + quantise"
+    res, q, s = ops.rmsnorm_quant_fp8(xd, wd, r=rd)
+    res2, normed2 = ops.add_rmsnorm(xd, rd, wd)
+    q2, s2 = ops.quantize_fp8(normed2)
+    assert torch.equal(res.view(torch.int16), res2.view(torch.int16))
+    assert float(s.item()) == float(s2.item()) and torch.equal(bytes_of(q), bytes_of(q2)), "add + norm + quantise"
+
+
+@pytest.mark.parametrize("qrows", [1, 2, 4])
+def test_norm_quant_pass_layouts_agree(ops, qrows):
+    """The e4m3 pass handles 1, 2 or 4 rows per CTA: same bytes from all, including from a source that is only
+    16-byte aligned."""
     try:
-        ops.tune("quant.wide", wide)
         ops.tune("quant.rows_per_cta", qrows)
         for T, cols in ((1027, 3136), (3, 16), (50, 4096), (9, 8200)):
             x, r, w = og.cfg1_inputs(T, cols)
@@ -127,7 +144,6 @@ def test_norm_quant_pass_layouts_agree(ops, wide, qrows):
             q4, s4 = ops.quantize_fp8(ops.rmsnorm(xd, wd))
             assert float(s3.item()) == float(s4.item()) and torch.equal(bytes_of(q3), bytes_of(q4)), (T, cols)
     finally:
-        ops.tune("quant.wide", 0)
         ops.tune("quant.rows_per_cta", 0)
 
 

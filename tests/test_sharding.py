@@ -30,6 +30,30 @@ def test_schedule_and_byte_model():
     assert chain.bytes_per_token(8) == 2693384
 
 
+def test_batch_shard_rows_do_not_depend_on_the_split():
+    """bench.py splits ONE seeded batch: the rows a rank generates for [lo, hi) are the rows of the whole batch,
+    for every world size, also when a shard boundary falls inside a generation block."""
+    total, vocab = 2 * chain.BATCH_BLOCK_ROWS + 37, 64
+    whole = chain.batch_shard(total, 0, total, "cpu", seed=3, vocab=vocab)
+    assert whole["ids"].dtype == torch.int32 and int(whole["ids"].max()) < vocab and int(whole["ids"].min()) >= 0
+    assert whole["y"].shape == (total, chain.D_INNER) and whole["u"].dtype == torch.bfloat16
+    for world in (2, 3, 8):
+        for rank in range(world):
+            lo, hi = chain.shard_range(total, rank, world)
+            part = chain.batch_shard(total, lo, hi, "cpu", seed=3, vocab=vocab)
+            for key in ("ids", "y", "z", "u"):
+                assert torch.equal(part[key], whole[key][lo:hi]), (key, world, rank)
+            for a, b in zip(part["mixer_out"], whole["mixer_out"]):
+                assert torch.equal(a, b[lo:hi])
+            for key in ("table", "norm_w", "gated_w"):
+                assert torch.equal(part[key], whole[key])
+    other = chain.batch_shard(total, 0, 16, "cpu", seed=4, vocab=vocab)
+    assert not torch.equal(other["y"], whole["y"][:16])
+    assert chain.batch_shard(total, 5, 5, "cpu", seed=3, vocab=vocab)["y"].shape[0] == 0
+    with pytest.raises(ValueError):
+        chain.batch_shard(10, 4, 11, "cpu")
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

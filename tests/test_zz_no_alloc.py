@@ -55,6 +55,27 @@ def test_static_scratch_form_matches_workspace_form_twice_in_a_row(built_lib):
     assert _run_both(lib, *second)[1][2] < _run_both(lib, *first)[1][2]
 
 
+def test_static_scratch_form_at_exactly_the_row_limit(built_lib):
+    """rows == NMT_STATIC_SCRATCH_MAX_ROWS writes the last float of the built-in array: the only size at which a
+    miscounted array length would show.  Narrow rows keep the case at about a megabyte per tensor."""
+    lib = built_lib
+    assert lib.nmt_set_device(torch.cuda.current_device()) == 0
+    g = torch.Generator().manual_seed(65536)
+    x = torch.randn(MAX_ROWS, 8, generator=g).to(BF).cuda()
+    r = torch.randn(MAX_ROWS, 8, generator=g).to(BF).cuda()
+    x[MAX_ROWS - 1] = 3.0 * x[MAX_ROWS - 1]                      # the last row carries a rstd of its own
+    w = og.norm_weight(8, g).cuda()
+    for _ in range(2):
+        (res_ws, q_ws, s_ws), (res_st, q_st, s_st) = _run_both(lib, x, r, w)
+        assert torch.equal(res_st.view(torch.int16), res_ws.view(torch.int16))
+        assert s_st == s_ws and s_st > 0.0
+        assert torch.equal(q_st, q_ws)
+    want_res, want = og.add_rmsnorm_bf16(x.cpu(), r.cpu(), w.cpu())
+    q_want, s_want = og.quantize_fp8(want)
+    assert torch.equal(res_st.cpu().view(torch.int16), want_res.view(torch.int16))
+    assert abs(s_st - float(s_want)) <= 1e-6 * float(s_want) + 1e-12
+
+
 def test_static_scratch_form_rejects_too_many_rows_and_allocates_nothing(built_lib):
     lib = built_lib
     lib.nmt_set_device(torch.cuda.current_device())
