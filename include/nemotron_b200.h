@@ -89,6 +89,38 @@ int nmt_add_rmsnorm_bf16(const void* x, const void* r, const float* w,
                          void* out_res, void* out,
                          int64_t rows, int64_t cols, float eps, void* stream);
 
+/* ---- Residual add of block i fused with the pre-norm of block i+1, block code unchanged ------------------ */
+
+/* Every reference block is out = input + mixer(rmsnorm(input)): it opens with rmsnorm_bf16 into its first
+ * workspace tensor (model/mlp_block.cuh:98, model/mamba_block.cuh:183, model/attention_block.cuh:196) and closes
+ * with the residual add (model/mlp_block.cuh:104, model/mamba_block.cuh:224, model/attention_block.cuh:210), whose
+ * output the next block's rmsnorm re-reads at once.  These entry points fuse that pair ACROSS two block calls
+ * without changing a block, a binding or a signature.  They have no counterpart in the reference.
+ *
+ *   nmt_fuse_next_norm(w_next, eps)   called by the orchestrator (engine.py's layer loop) before it calls block i:
+ *                                     announces the norm weight of block i+1.  NULL withdraws the announcement.
+ *   nmt_block_head_rmsnorm_bf16       what the drop-in rmsnorm_bf16 calls: nmt_rmsnorm_bf16, except that it launches
+ *                                     NOTHING when the previous block's fused tail already wrote exactly this tensor
+ *                                     (same x, y, w, shape, eps and stream).
+ *   nmt_block_tail_add_bf16           what the drop-in residual add calls: nmt_add_bf16, except that with a weight
+ *                                     announced it launches nmt_add_rmsnorm_bf16 instead and writes rmsnorm(out) *
+ *                                     w_next over THIS block's pre-norm tensor (the y of its head call).
+ * Requirements, all met by the reference's blocks under engine.py: the block's pre-norm tensor is not read after
+ * the block's closing add on that stream (its readers are the block's first projections); the next block's
+ * pre-norm tensor has the same address, which the bump allocator guarantees once it is rewound before every layer
+ * (engine.py:263, tensor/allocator.cuh:124-129); nothing else writes that address between the two block calls.
+ * Whatever does not match runs the plain kernels - same results, one more pass over the rows.  Announce only when
+ * the next block really opens with rmsnorm_bf16 on the tensor this block writes (not ahead of a block form that
+ * fuses its own norm, nor after the last layer unless the final norm writes into that same workspace).
+ * State is per host thread.  nmt_fusion_reset() forgets an announcement and a pending fused tail (call it when a
+ * pass is abandoned half way); nmt_fusion_counters reports how many tails were fused and heads skipped. */
+int nmt_fuse_next_norm(const float* next_norm_w, float eps);
+int nmt_fusion_reset(void);
+int nmt_fusion_counters(int64_t* fused_tails, int64_t* elided_heads);
+int nmt_block_head_rmsnorm_bf16(const void* x, void* y, const float* w,
+                                int64_t rows, int64_t cols, float eps, void* stream);
+int nmt_block_tail_add_bf16(const void* a, const void* b, void* out, int64_t n, void* stream);
+
 /* ---- Mamba-2 gated RMSNorm ------------------------------------------------ */
 
 /* g = y * silu(z); per group of `group_size` channels:
@@ -275,6 +307,11 @@ int nmt_tune_get(const char* key, int* value);
  * kernel winds down instead of spinning.  Returns the number of such timeouts on the current device since
  * load (synchronises the device; 0 in a healthy run, -1 if the counter cannot be read). */
 int64_t nmt_device_wait_timeouts(void);
+/* Exercises that path without involving a product kernel: one thread of a 32-thread CTA waits, for at most `polls`
+ * polls (1..4096), on an mbarrier in its own shared memory that nothing will ever complete.  The wait gives up after
+ * microseconds, nmt_device_wait_timeouts() rises by one, *gave_up_device (device int32, may be NULL) is set to 1, and
+ * the context stays usable.  Has no counterpart in the reference. */
+int nmt_selftest_wait_runs_out(int polls, int* gave_up_device, void* stream);
 /* Number of kernel launches this library has enqueued since load (all threads). */
 int64_t nmt_launch_count(void);
 

@@ -3,6 +3,11 @@
 // reference it does not range-check the ids; use nmt_embedding_bf16_i64 directly to get the checked form.
 #ifndef NEMOTRON_B200_SHIM_EMBEDDING_CUH
 #define NEMOTRON_B200_SHIM_EMBEDDING_CUH
+// The reference's own guard: wherever its header of the same name is included later (binding.cu includes it by a path
+// relative to itself), it is skipped, so the launchers below are the only definitions.
+#ifndef NEMOTRON_INFER_EMBEDDING_CUH
+#define NEMOTRON_INFER_EMBEDDING_CUH
+#endif
 
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>

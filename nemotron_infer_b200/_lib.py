@@ -27,6 +27,11 @@ PROTOTYPES = {
     "nmt_rmsnorm_f32": (_int, [_p, _p, _p, _i64, _i64, _f, _p]),
     "nmt_rmsnorm_bf16": (_int, [_p, _p, _p, _i64, _i64, _f, _p]),
     "nmt_add_rmsnorm_bf16": (_int, [_p, _p, _p, _p, _p, _i64, _i64, _f, _p]),
+    "nmt_fuse_next_norm": (_int, [_p, _f]),
+    "nmt_fusion_reset": (_int, []),
+    "nmt_fusion_counters": (_int, [C.POINTER(_i64), C.POINTER(_i64)]),
+    "nmt_block_head_rmsnorm_bf16": (_int, [_p, _p, _p, _i64, _i64, _f, _p]),
+    "nmt_block_tail_add_bf16": (_int, [_p, _p, _p, _i64, _p]),
     "nmt_rmsnorm_gated_bf16": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _f, _p]),
     "nmt_rmsnorm_gated_f32": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _f, _p]),
     "nmt_relu2_bf16": (_int, [_p, _p, _i64, _p]),
@@ -49,6 +54,7 @@ PROTOTYPES = {
     "nmt_add_rmsnorm_quant_fp8_static": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _f, _p]),
     "nmt_tune_set": (_int, [C.c_char_p, _int]),
     "nmt_tune_get": (_int, [C.c_char_p, C.POINTER(_int)]),
+    "nmt_selftest_wait_runs_out": (_int, [_int, _p, _p]),
     "nmt_launch_count": (_i64, []),
     "nmt_device_wait_timeouts": (_i64, []),
 }

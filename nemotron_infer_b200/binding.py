@@ -10,7 +10,9 @@ anything, a rejected argument raises `NemotronB200Error` and launches nothing.
 Reference names kept: embedding, rmsnorm, sync, reset_allocator, free_allocator
 and the model constants.  Added (the fused forms the reference spreads over two
 block calls, and the ops its blocks call internally): add_rmsnorm,
-rmsnorm_gated, relu2, add.
+rmsnorm_gated, relu2, add; and fuse_next_norm / fusion_reset / fusion_counters,
+the announcement that lets the reference's unchanged blocks (built on the drop-in
+headers) fuse the residual add of one layer with the pre-norm of the next.
 """
 from __future__ import annotations
 
@@ -91,3 +93,24 @@ def relu2(u: int, out: int, M: int, width: int = INTER) -> None:
 def add(a: int, b: int, out: int, M: int, width: int = HIDDEN) -> None:
     """out = a + b over [M, width] (the residual add, model/mlp_block.cuh:104)."""
     _lib.check(_lib.load().nmt_add_bf16(a, b, out, M * width, _stream), "add")
+
+
+def fuse_next_norm(next_norm_w: int | None) -> None:
+    """Announces, before block i is called, the device address of block i+1's norm weight (None withdraws it).
+    The reference's blocks built on include/nemotron_b200_shim then run block i's closing residual add
+    (model/mlp_block.cuh:104) and block i+1's pre-norm (model/mlp_block.cuh:98) as one launch; engine.py's layer
+    loop (engine.py:262-270) only gains this call.  See nmt_fuse_next_norm in include/nemotron_b200.h."""
+    _lib.check(_lib.load().nmt_fuse_next_norm(next_norm_w or None, EPS), "fuse_next_norm")
+
+
+def fusion_reset() -> None:
+    """Forgets an announcement and a pending fused tail (call when a pass is abandoned half way)."""
+    _lib.check(_lib.load().nmt_fusion_reset(), "fusion_reset")
+
+
+def fusion_counters() -> tuple[int, int]:
+    """(residual adds that ran fused with the next norm, pre-norms that were skipped) on this thread so far."""
+    import ctypes as C
+    a, b = C.c_int64(0), C.c_int64(0)
+    _lib.check(_lib.load().nmt_fusion_counters(C.byref(a), C.byref(b)), "fusion_counters")
+    return a.value, b.value

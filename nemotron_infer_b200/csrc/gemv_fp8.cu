@@ -4,24 +4,24 @@
 // whole model, ops/gemv.cuh:4-6): the only thing that matters is how fast W crosses HBM, and a matrix is gone in
 // a few microseconds, so every SM has to have deep loads in flight from its first cycle.
 //
-// Three kernels live here.  The default (gemv_w8a16_mma_kernel, further down) runs the inner product on
-// mma.sync and needs K % 64 == 0; the two CUDA-core kernels that come first are the general fallback (any K that
-// is a multiple of 16) and keep exact fp32 products for every x ("gemv.variant" = 1 / 2).  Common to all:
-//   * Persistent grid, one CTA of 8 warps per SM slot.  x is converted to fp32 once per CTA into shared memory
-//     (16 floats per 16 weights come back as four LDS.128, no per-use unpacking).
-//   * A work unit is (row, K-slice): rows are cut into SPLIT slices of ~3 KB so that short-and-wide matrices
-//     (down_proj: 3136 rows of 12544) still give every warp several units; the SPLIT warps that share a row sit
+// Kernels, in the order of the file: two CUDA-core kernels (the general fallback: any K that is a multiple of 16, exact
+// fp32 products for every x; "gemv.variant" = 1 / 2), the register-streaming tensor-core kernel
+// (gemv_w8a16_mma_kernel, "gemv.variant" = 3: K % 64 == 0, any K that fits shared memory as f16) and the default,
+// gemv_w8a16_ring_kernel ("gemv.variant" = 4: K % 64 == 0, K <= 16384), which feeds the same MMA fragments from a
+// shared-memory ring filled by bulk copies.  Common to all:
+//   * Persistent grid.  x is converted once per CTA into shared memory.
+//   * A work unit is (rows, K-slice): rows are cut into slices of a few KB so that short-and-wide matrices
+//     (down_proj: 3136 rows of 12544) still give every warp several units; the warps that share a row sit
 //     in one CTA and combine their partial sums through shared memory in a fixed order (deterministic).
-//   * Each lane issues all 16-byte weight loads of its unit before the first use, and the next unit's before the
-//     arithmetic of the current one; consecutive lanes read consecutive 16 bytes.  e4m3 pairs go to f16x2 with
-//     one cvt (exact), then to fp32, and accumulate with f32x2 FMAs in fp32 -- the arithmetic the reference
-//     specifies (ops/gemv.cuh:20-22), no fp16 accumulation.
+//   * fp32 accumulation throughout -- the arithmetic the reference specifies (ops/gemv.cuh:20-22), no fp16 accumulation.
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
-#include "nmt_common.cuh"
+#include "nmt_tma.cuh"
 
 namespace nmt {
+
+NMT_DEFINE_TIMEOUT_READER();
 
 constexpr int kGemvWarps = 8;
 
@@ -522,6 +522,280 @@ static int launch_gemv_mma_auto(const void* x, const void* W, const float* w_sca
     return NMT_ERR_UNSUPPORTED;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Shared-memory ring.  The register-streaming kernel above keeps its bytes in flight in registers (two load groups of
+// four 16-byte vectors for two A-rows: 64 registers), which caps it at 16 warps per SM and ~50 KB in flight per SM;
+// it runs at 3.6-4.0 TB/s on the model's matrices.  Here the weight stream never touches a register before it is
+// used: consecutive matrix rows are one contiguous range of W, so a STAGE (128 / Q rows, 16-32 KB) is brought in by a
+// single producer lane with cp.async.bulk (one copy per stage, or one per row where rows need a 64-byte skew in
+// shared memory to stay bank-conflict free), completing on the stage's mbarrier; the eight consumer warps take a
+// stage from shared memory with the same permuted-k MMA fragments, 16 bytes per lane per A-row, and hand it back
+// through a second mbarrier.  The ring is full from the kernel's first cycle - before x is staged and before the
+// wait on the preceding kernel - and the last copies are issued long before the last stage is consumed, so the
+// dependent launch can be triggered early.  Every wait is bounded (nmt_tma.cuh); a wait that runs out is counted,
+// the CTA stops waiting, finishes its loop on whatever is in shared memory (its results are void) and the producer
+// drains the copies it has in flight before the CTA leaves.
+//
+// Geometry: Q = S * SPLIT slices per row as above; a warp tile is R = 16 / S rows, a stage TILES = 8 / SPLIT warp
+// tiles, i.e. 128 / Q rows.  Q is chosen so that a slice is 2-4 chunks, which makes a stage 16-32 KB for every K.
+// ---------------------------------------------------------------------------------------------
+constexpr int kRingMaxStages = 8;
+constexpr int kRingThreads = (kGemvWarps + 1) * 32;               // eight consumer warps and the producer warp
+
+__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kGemvWarps * 32) : "memory"); }
+
+__host__ __device__ constexpr int ring_row_stride(int K) { return K + ((K % 128) == 0 ? 64 : 0); }
+
+template <int SPLIT, int S>
+__global__ void __launch_bounds__(kRingThreads, 2)
+gemv_w8a16_ring_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, const float* __restrict__ w_scale,
+                       __nv_bfloat16* __restrict__ y, int N, int K, int stages, int early_trigger, GemvFusion fu) {
+    constexpr int R = 16 / S;
+    constexpr int TILES = kGemvWarps / SPLIT;
+    constexpr int ROWS = R * TILES;                                // matrix rows per stage
+    constexpr int Q = S * SPLIT;                                   // k-slices per matrix row
+    constexpr int NC = kGemvWarps * 32;                            // consumer threads
+    extern __shared__ __align__(128) uint8_t smem_b[];
+    __shared__ uint64_t s_full[kRingMaxStages], s_empty[kRingMaxStages];
+    __shared__ float s_red[kGemvWarps];
+    __shared__ float s_part[2][kGemvWarps][16];
+    __shared__ int s_abort;
+    const int Kp = ring_row_stride(K);
+    const size_t stage_stride = (size_t)ROWS * Kp;
+    uint8_t* ring = smem_b;
+    __half* xh = reinterpret_cast<__half*>(smem_b + (size_t)stages * stage_stride);     // K halves, then 64 halves of zero
+    uint32_t* xn = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(xh) + mma_x_bytes(K));   // K bf16: the normalised x
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nstages_total = (N + ROWS - 1) / ROWS;
+    const int mine = nstages_total > (int)blockIdx.x ? (nstages_total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    int issued = 0;                                                // producer lane: fills whose copies have been issued
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], kGemvWarps); }
+        s_abort = 0;
+        mbar_init_fence();
+    }
+    __syncthreads();
+
+    if (warp == kGemvWarps) {
+        // ---------------- producer: one lane keeps the ring full ----------------
+        // The weights are constants of the model, not an output of the preceding kernel: their copies go out without
+        // waiting for that kernel.
+        if (lane == 0) {
+            bool ok = true;
+            for (int n = 0; n < mine && ok; ++n) {
+                const int s = n % stages;
+                if (n >= stages) ok = mbar_wait(&s_empty[s], static_cast<uint32_t>(n / stages - 1) & 1u);
+                if (!ok) break;
+                const int64_t row0 = ((int64_t)blockIdx.x + (int64_t)n * gridDim.x) * ROWS;
+                const int rows = static_cast<int>(min((int64_t)ROWS, (int64_t)N - row0));
+                uint8_t* dst = ring + (size_t)s * stage_stride;
+                const uint8_t* src = W + (size_t)row0 * K;
+                mbar_arrive_expect_tx(&s_full[s], static_cast<uint32_t>(rows) * static_cast<uint32_t>(K));
+                if (Kp == K) {
+                    bulk_load(dst, src, static_cast<uint32_t>(rows) * static_cast<uint32_t>(K), &s_full[s]);
+                } else {
+                    for (int r = 0; r < rows; ++r) bulk_load(dst + (size_t)r * Kp, src + (size_t)r * K, static_cast<uint32_t>(K), &s_full[s]);
+                }
+                issued = n + 1;
+            }
+            if (early_trigger) pdl_trigger();                      // every copy of this CTA has been issued
+            if (!ok) atomicExch(&s_abort, 1);                      // counted by mbar_wait; the consumers stop waiting too
+        }
+    } else {
+        // ---------------- consumers ----------------
+        const int g = lane >> 2, t = lane & 3;
+        const int kc = K / 64;
+        const int base = kc / Q, rem = kc % Q;
+        auto slice_start = [&](int q) { return q * base + max(0, q - (Q - rem)); };
+        auto slice_len = [&](int q) { return base + (q >= Q - rem ? 1 : 0); };
+        const int split_id = warp % SPLIT, tile_in_cta = warp / SPLIT;
+        const int sA = g / R, rA = g % R, sB = (g + 8) / R, rB = (g + 8) % R;
+        const int cA0 = slice_start(split_id * S + sA), cB0 = slice_start(split_id * S + sB);
+        const int cX0 = g < S ? slice_start(split_id * S + g) : 0, nX = g < S ? slice_len(split_id * S + g) : 0;
+        const int nmax = base + (rem ? 1 : 0);
+        const __half* xzero = xh + K;
+        const __half* xbase = xh + (size_t)cX0 * 64 + t * 16;
+        const size_t offA = (size_t)(tile_in_cta * R + rA) * Kp + (size_t)cA0 * 64 + t * 16;
+        const size_t offB = (size_t)(tile_in_cta * R + rB) * Kp + (size_t)cB0 * 64 + t * 16;
+
+        pdl_wait();                                                // x (and the residual) may come from the preceding kernel
+
+        // ---- stage x: (optional RMSNorm) -> max|x| -> power-of-two scale -> f16; the ring fills meanwhile ----
+        const uint32_t* xw = reinterpret_cast<const uint32_t*>(x);
+        const int words = K / 2;
+        const bool normed = fu.norm_w != nullptr;                  // block-uniform
+        if (normed) {
+            // The stand-alone kernel's shape (rmsnorm_ctarow_kernel, one row): norm_threads threads, thread t owns
+            // vectors t, t + norm_threads, ...; per-thread f32x2 sums, warp shuffle, then the warps in order.
+            const int nt = fu.norm_threads, nv = K / 8;
+            const uint4* xv = reinterpret_cast<const uint4*>(x);
+            uint4 a[8];
+            if (threadIdx.x < nt) {
+                float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int v = q * nt + threadIdx.x;
+                    a[q] = v < nv ? ld_stream(xv + v) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    float2 pr[4];
+                    unpack8x2(a[q], pr);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) acc = __ffma2_rn(pr[k], pr[k], acc);
+                }
+                const float ss = warp_sum(acc.x + acc.y);
+                if (lane == 0) s_red[warp] = ss;
+            }
+            consumer_barrier();
+            if (threadIdx.x < nt) {
+                float total = 0.f;
+                for (int i = 0; i < nt / 32; ++i) total += s_red[i];
+                const float rstd = rsqrtf(total * fu.inv_cols + fu.eps);
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const int v = q * nt + threadIdx.x;
+                    if (v < nv) {
+                        float2 pr[4];
+                        unpack8x2(a[q], pr);
+                        reinterpret_cast<uint4*>(xn)[v] = scale8(pr, rstd, ld_weight4(fu.norm_w + (size_t)v * 8), ld_weight4(fu.norm_w + (size_t)v * 8 + 4));
+                    }
+                }
+            }
+            consumer_barrier();
+        }
+        constexpr int XW = 32;                                     // words (bf16 pairs) per thread held in registers: K <= 16384
+        uint32_t xr[XW];
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < XW; ++i) {
+            const int idx = threadIdx.x + i * NC;
+            xr[i] = idx < words ? (normed ? xn[idx] : __ldg(xw + idx)) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < XW; ++i) m = fmaxf(m, fmaxf(fabsf(bf16_lo(xr[i])), fabsf(bf16_hi(xr[i]))));
+        m = warp_max(m);
+        if (lane == 0) s_red[warp] = m;
+        consumer_barrier();
+        float mm = 0.f;
+#pragma unroll
+        for (int i = 0; i < kGemvWarps; ++i) mm = fmaxf(mm, s_red[i]);
+        int e = 0;
+        if (mm > 0.f && mm < 3.0e38f) e = static_cast<int>((__float_as_uint(mm) >> 23) & 0xff) - 127 - 14;   // max|x| lands in [2^14, 2^15)
+        e = max(e, -100);                                          // keeps 2^-e and 2^e normal fp32 numbers
+        const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);      // 2^-e
+        const float up = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);        // 2^e
+#pragma unroll
+        for (int i = 0; i < XW; ++i) {
+            const int idx = threadIdx.x + i * NC;
+            if (idx < words) reinterpret_cast<__half2*>(xh)[idx] = __floats2half2_rn(bf16_lo(xr[i]) * down, bf16_hi(xr[i]) * down);
+        }
+        if (threadIdx.x < 32) reinterpret_cast<uint32_t*>(xh + K)[threadIdx.x] = 0u;
+        consumer_barrier();
+
+        // ---- consume the ring ----
+        bool waiting = true;                                       // false once a wait has run out anywhere in the CTA
+#pragma unroll 1
+        for (int n = 0; n < mine; ++n) {
+            const int s = n % stages;
+            if (waiting) {
+                if (*reinterpret_cast<volatile int*>(&s_abort) != 0) waiting = false;
+                else if (!mbar_wait(&s_full[s], static_cast<uint32_t>(n / stages) & 1u)) { waiting = false; atomicExch(&s_abort, 1); }
+            }
+            const uint8_t* st = ring + (size_t)s * stage_stride;
+            float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};    // two chains, so an MMA does not wait for the one before it
+#pragma unroll 4
+            for (int j = 0; j < nmax; ++j) {
+                const uint4 wa = lds128(st + offA + (size_t)j * 64);
+                const uint4 wb = lds128(st + offB + (size_t)j * 64);
+                const uint4* xp = reinterpret_cast<const uint4*>(j < nX ? xbase + j * 64 : xzero);
+                const uint4 x0 = xp[0], x1 = xp[1];
+                const uint32_t wa_[4] = {wa.x, wa.y, wa.z, wa.w};
+                const uint32_t wb_[4] = {wb.x, wb.y, wb.z, wb.w};
+                const uint32_t xb_[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                    mma_f16((q & 1) ? d : c, e4m3_lo(wa_[q]), e4m3_lo(wb_[q]), e4m3_hi(wa_[q]), e4m3_hi(wb_[q]), xb_[2 * q], xb_[2 * q + 1]);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_empty[s]);               // this warp is done with the stage's bytes
+            // C[a][n] is wanted for n = stream(a) only: lane (g, t) holds columns 2t, 2t+1 of A-rows g and g+8
+            float* pw = s_part[n & 1][warp];
+            if (sA / 2 == t) pw[g] = c[sA & 1] + d[sA & 1];
+            if (sB / 2 == t) pw[g + 8] = c[2 + (sB & 1)] + d[2 + (sB & 1)];
+            consumer_barrier();
+            // matrix row r of warp tile tc = sum over the split warps and streams, in a fixed order
+            if (threadIdx.x < ROWS) {
+                const int tc = threadIdx.x / R, r = threadIdx.x % R;
+                const int64_t row = ((int64_t)blockIdx.x + (int64_t)n * gridDim.x) * ROWS + threadIdx.x;
+                if (row < N) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int sp = 0; sp < SPLIT; ++sp)
+#pragma unroll
+                        for (int s2 = 0; s2 < S; ++s2) sum += s_part[n & 1][tc * SPLIT + sp][s2 * R + r];
+                    // bf16 result in the low half of a pair, so the epilogues can use the stand-alone kernels' instructions
+                    uint32_t yb = pack_bf16x2((sum * up) * __ldg(w_scale + row), 0.f);
+                    if (fu.activation == 1) yb = relu2_bf16x2(yb);
+                    if (fu.residual) yb = add_bf16x2_rn(static_cast<uint32_t>(fu.residual[row]), yb);
+                    reinterpret_cast<uint16_t*>(y)[row] = static_cast<uint16_t>(yb & 0xffffu);
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // A wait ran out somewhere in this CTA (counted; its results are void): the consumers may have gone through the
+    // ring without waiting, so copies may still be in flight.  The producer lane does not leave - and the CTA's shared
+    // memory is not released - before the last fill of every stage has landed (bounded waits again).
+    if (warp == kGemvWarps && lane == 0 && *reinterpret_cast<volatile int*>(&s_abort) != 0) {
+        for (int n = max(0, issued - stages); n < issued; ++n)
+            mbar_wait(&s_full[n % stages], static_cast<uint32_t>(n / stages) & 1u);
+    }
+    pdl_trigger();
+}
+
+template <int SPLIT, int S>
+static int launch_gemv_ring(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
+    constexpr int R = 16 / S, TILES = kGemvWarps / SPLIT, ROWS = R * TILES;
+    auto kern = gemv_w8a16_ring_kernel<SPLIT, S>;
+    const size_t stage_stride = (size_t)ROWS * ring_row_stride(K);
+    const size_t fixed = mma_x_bytes(K) + (fu.norm_w ? (size_t)K * 2 : 0);
+    int stages = tune("gemv.ring_stages", 3);         // 3 leaves room for the next launch's CTA beside this one
+    if (stages > kRingMaxStages) stages = kRingMaxStages;
+    while (stages > 2 && stages * stage_stride + fixed > 200 * 1024) --stages;
+    const size_t smem = stages * stage_stride + fixed;
+    if (stages < 2 || smem > 200 * 1024) return NMT_ERR_UNSUPPORTED;
+    const int nstages_total = (N + ROWS - 1) / ROWS;
+    const int per_sm = tune("gemv.ctas_per_sm", 1) >= 2 && 2 * smem <= 220 * 1024 ? 2 : 1;   // two only where both fit an SM
+    const int grid = nstages_total < kSmCount * per_sm ? nstages_total : kSmCount * per_sm;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return finish_launch(0);
+        configured[dev] = true;
+    }
+    launch_kernel(kern, grid, kRingThreads, smem, st, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(W), w_scale,
+                  static_cast<__nv_bfloat16*>(y), N, K, stages, tune("gemv.early_trigger", 1) == 1, fu);
+    return finish_launch(1);
+}
+
+// Slices per row so that a slice is 2-4 chunks (a stage 16-32 KB); all eight warps share one warp tile when the row
+// is long enough.  NMT_ERR_UNSUPPORTED when x does not fit the register staging (K > 16384) or K % 64 != 0.
+static int launch_gemv_ring_auto(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
+    if ((K % 64) != 0 || K > 16384) return NMT_ERR_UNSUPPORTED;
+    const int kc = K / 64;
+    int q = 1;
+    while (q < 64 && (kc + q - 1) / q > tune("gemv.unit_chunks", 4)) q *= 2;
+    const int split = q >= 8 ? 8 : q, streams = q / split;
+#define NMT_RING_CASE(SP, ST) if (split == SP && streams == ST) return launch_gemv_ring<SP, ST>(x, W, w_scale, y, N, K, fu, st)
+    NMT_RING_CASE(1, 1); NMT_RING_CASE(2, 1); NMT_RING_CASE(4, 1);
+    NMT_RING_CASE(8, 1); NMT_RING_CASE(8, 2); NMT_RING_CASE(8, 4); NMT_RING_CASE(8, 8);
+#undef NMT_RING_CASE
+    return NMT_ERR_UNSUPPORTED;
+}
+
 template <int SPLIT>
 static int launch_gemv(const void* x, const void* W, const float* w_scale, void* y, int N, int kv, cudaStream_t st) {
     constexpr int UNROLL = 4;
@@ -569,6 +843,11 @@ int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, con
     fu.residual = static_cast<const uint16_t*>(residual_bf16);
     // The prologue keeps a thread's share of x in 8 registers-vectors; the fused forms exist only on the tensor-core kernel.
     if (norm_w && (fu.norm_threads > kGemvWarps * 32 || (K / 8 + fu.norm_threads - 1) / fu.norm_threads > 8)) return NMT_ERR_UNSUPPORTED;
+    if (tune("gemv.variant", 4) == 4) {          // 4 = shared-memory ring (default), 3 = register streaming
+        const int r = launch_gemv_ring_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
+                                            static_cast<cudaStream_t>(stream));
+        if (r != NMT_ERR_UNSUPPORTED) return r;
+    }
     return launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
                                 static_cast<cudaStream_t>(stream));
 }
@@ -583,7 +862,12 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
     if (K > 45000) return NMT_ERR_UNSUPPORTED;                        // x must fit shared memory as fp32
     const int kv = static_cast<int>(K / 16);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (tune("gemv.variant", 3) == 3) {          // 3 = tensor-core inner product (default), 1 / 2 = CUDA-core kernels
+    const int variant = tune("gemv.variant", 4); // 4 = shared-memory ring (default), 3 = register streaming, 1 / 2 = CUDA-core kernels
+    if (variant == 4) {
+        const int r = launch_gemv_ring_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), GemvFusion{}, st);
+        if (r != NMT_ERR_UNSUPPORTED) return r;
+    }
+    if (variant >= 3) {
         const int r = launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), GemvFusion{}, st);
         if (r != NMT_ERR_UNSUPPORTED) return r;
     }

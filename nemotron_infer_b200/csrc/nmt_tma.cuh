@@ -48,13 +48,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs) : "memory");
     return ok != 0;
 }
-// Returns false (and counts a timeout) if the phase did not complete within the spin limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i)
+// Returns false (and counts a timeout) if the phase did not complete within `limit` polls.
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, uint32_t limit) {
+    for (uint32_t i = 0; i < limit; ++i)
         if (mbar_try_wait(bar, parity)) return true;
     atomicAdd(&g_wait_timeouts, 1u);
     return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_limited(bar, parity, kSpinLimit); }
 
 // global -> shared bulk copy; completion (byte count) is signalled on `bar`.
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {

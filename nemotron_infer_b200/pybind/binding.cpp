@@ -86,5 +86,14 @@ PYBIND11_MODULE(binding, m) {
         check(nmt_quantize_fp8(cp(x), mp(out), reinterpret_cast<float*>(scale), reinterpret_cast<unsigned int*>(amax), n,
                                g_stream), "quantize_fp8");
     });
+    m.def("fuse_next_norm", [](uintptr_t next_norm_w) { check(nmt_fuse_next_norm(fp(next_norm_w), cfg::EPS), "fuse_next_norm"); },
+          "announce block i+1's norm weight (0 withdraws) before calling block i: the reference's blocks built on the "
+          "drop-in headers then fuse block i's residual add with block i+1's pre-norm");
+    m.def("fusion_reset", [] { check(nmt_fusion_reset(), "fusion_reset"); });
+    m.def("fusion_counters", [] {
+        int64_t fused = 0, skipped = 0;
+        check(nmt_fusion_counters(&fused, &skipped), "fusion_counters");
+        return py::make_tuple(fused, skipped);
+    });
     m.def("version", [] { return std::string(nmt_version()); });
 }

@@ -84,6 +84,14 @@ def relu2_bf16(u: torch.Tensor) -> torch.Tensor:
     return relu2(u).to(torch.bfloat16)
 
 
+# --- the whole MLP block (tools/dump_mlp_block.py:42-53), used as the golden of stacked-block tests ------------
+
+def mlp_block(x: torch.Tensor, norm_w: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor, eps: float = EPS) -> torch.Tensor:
+    """out = x + down(relu(up(rmsnorm(x)))^2), fp32, weights in nn.Linear layout [out, in]."""
+    x = x.float()
+    return residual_add(x, F.linear(relu2(F.linear(plain_rmsnorm(x, norm_w, eps), up_w)), down_w))
+
+
 # --- Mamba-2 depthwise causal conv1d + SiLU (tools/dump_mamba_block.py:126-130; tools/ref_full_model.py mamba()) ---
 
 def causal_conv1d_silu(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor) -> torch.Tensor:

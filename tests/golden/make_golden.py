@@ -22,7 +22,8 @@ Two sources, neither of which copies reference text into this repository:
    rounded before the norm).  relu^2 / residual add / embedding use the same
    torch expressions the emitters use (F.relu(u).pow(2), a + b, F.embedding).
 
-Outputs: dump_mlp_block.npz, dump_mamba_block.npz, cfg_bf16.npz, cfg0_fp32.npz.
+Outputs: dump_mlp_block.npz, dump_mamba_block.npz, dump_attention_block.npz (tools/dump_attention_block.py, run
+unmodified the same way: input, the five weights, normed, expected), cfg_bf16.npz, cfg0_fp32.npz.
 bf16 tensors are stored as their uint16 bit patterns.
 """
 from __future__ import annotations
@@ -88,6 +89,10 @@ def main() -> None:
     keep = ["input", "block_norm_w", "in_proj_w", "conv1d_w", "conv1d_b", "A_log", "D", "dt_bias", "gnorm_w", "out_proj_w",
             "normed", "xbc", "xbc_conv", "scan_y", "gate", "gnormed", "mixer_out", "expected", "meta"]
     np.savez_compressed(os.path.join(HERE, "dump_mamba_block.npz"), **{k: mam[k] for k in keep})
+
+    att = run_dump(a.reference, "dump_attention_block.py", "attention_block")
+    keep = ["input", "block_norm_w", "q_proj_w", "k_proj_w", "v_proj_w", "o_proj_w", "normed", "expected", "meta"]
+    np.savez_compressed(os.path.join(HERE, "dump_attention_block.npz"), **{k: att[k] for k in keep})
 
     ref = lift_functions(os.path.join(a.reference, "tools", "dump_mamba_block.py"), ["plain_rmsnorm", "gated_rmsnorm"])
     plain_rmsnorm, gated_rmsnorm = ref["plain_rmsnorm"], ref["gated_rmsnorm"]

@@ -126,3 +126,26 @@ def test_pybind_module_has_the_reference_surface(built_lib):
         B.rmsnorm(0, BUF, BUF, 4)
     with pytest.raises(TypeError):
         B.rmsnorm(BUF, BUF, BUF)                            # same arity as the reference
+
+
+def test_cross_block_fusion_entry_points_validate_and_count_without_launching(built_lib):
+    """The announcement / bookkeeping half of the cross-block fusion needs no device: a misaligned weight is refused,
+    NULL withdraws, rows == 0 goes through the head and tail entry points as a no-op, and nothing is counted."""
+    L = built_lib
+    before = L.nmt_launch_count()
+    a, b = ctypes.c_int64(-1), ctypes.c_int64(-1)
+    assert L.nmt_fusion_reset() == 0
+    assert L.nmt_fusion_counters(ctypes.byref(a), ctypes.byref(b)) == 0
+    fused0, skipped0 = a.value, b.value
+    assert L.nmt_fuse_next_norm(BUF, 1e-5) == 0
+    assert L.nmt_fuse_next_norm(BUF + 4, 1e-5) == 2
+    assert L.nmt_fuse_next_norm(None, 1e-5) == 0
+    assert L.nmt_fuse_next_norm(BUF, 1e-5) == 0
+    assert L.nmt_block_head_rmsnorm_bf16(BUF, BUF, BUF, 0, 3136, 1e-5, None) == 0
+    assert L.nmt_block_tail_add_bf16(BUF, BUF, BUF, 0, None) == 0
+    assert L.nmt_block_head_rmsnorm_bf16(None, BUF, BUF, 4, 3136, 1e-5, None) == 1
+    assert L.nmt_block_tail_add_bf16(BUF, BUF + 2, BUF, 64, None) == 2
+    assert L.nmt_fusion_counters(ctypes.byref(a), ctypes.byref(b)) == 0
+    assert (a.value, b.value) == (fused0, skipped0)
+    assert L.nmt_fusion_reset() == 0
+    assert L.nmt_launch_count() == before

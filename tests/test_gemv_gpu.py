@@ -103,8 +103,9 @@ def test_tensor_core_path_x_magnitudes(ops, scale):
     assert rep["mismatch_frac"] <= 0.05 and rep["max_ulp"] <= 4, rep
 
 
-@pytest.mark.parametrize("N,K", [(40, 64), (9, 192), (300, 16384), (50, 16448), (1000, 512), (17, 32704)])
-def test_tensor_core_path_slicing(ops, N, K):
+@pytest.mark.parametrize("N,K", [(40, 64), (9, 192), (300, 16384), (50, 16448), (1000, 512), (17, 32704), (5000, 3136),
+                                 (1237, 12544), (333, 7680), (148 * 8 + 1, 128)])
+def test_tensor_core_path_slicing(ops, built_lib, N, K):
     """Shapes that exercise one chunk per row, uneven slices, the register-held and re-read x staging, many
     k-streams per tile and ragged last tiles; every stream count the knob allows."""
     g = torch.Generator().manual_seed(N * 7 + K)
@@ -112,14 +113,25 @@ def test_tensor_core_path_slicing(ops, N, K):
     W, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
     want = og.gemv_w8a16(x, W, sc)
     try:
+        ops.tune("gemv.variant", 3)                  # the register-streaming kernel
         for streams in (0, 1, 2, 4, 8):
             for chunks in (0, 2, 4):
                 ops.tune("gemv.streams", streams)
                 ops.tune("gemv.unit_chunks", chunks)
                 check(ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()), want)
-    finally:
         ops.tune("gemv.streams", 0)
-        ops.tune("gemv.unit_chunks", 0)
+        ops.tune("gemv.variant", 4)                  # the shared-memory ring (default where K <= 16384)
+        for stages in (0, 2, 4, 8):
+            for chunks in (0, 2, 3, 7):
+                for per_sm in (0, 2):
+                    ops.tune("gemv.ring_stages", stages)
+                    ops.tune("gemv.unit_chunks", chunks)
+                    ops.tune("gemv.ctas_per_sm", per_sm)
+                    check(ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()), want)
+    finally:
+        for k in ("gemv.streams", "gemv.unit_chunks", "gemv.variant", "gemv.ring_stages", "gemv.ctas_per_sm"):
+            ops.tune(k, 0)
+    assert built_lib.nmt_device_wait_timeouts() == 0
 
 
 @pytest.mark.parametrize("N,K", [(12544, 3136), (3136, 12544), (17504, 3136), (3136, 7680), (40, 64), (16, 10240)])

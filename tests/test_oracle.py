@@ -24,6 +24,20 @@ def test_relu2_and_residual_match_mlp_dump_stages():
     torch.testing.assert_close(og.residual_add(_t(d["input"]), _t(d["down"])), _t(d["expected"]), rtol=0, atol=0)
 
 
+def test_mlp_block_formula_matches_mlp_dump_output():
+    d = golden("dump_mlp_block.npz")
+    got = og.mlp_block(_t(d["input"]).reshape(8, 64), _t(d["block_norm_w"]), _t(d["up_proj_w"]).reshape(256, 64),
+                       _t(d["down_proj_w"]).reshape(64, 256))
+    torch.testing.assert_close(got.reshape(-1), _t(d["expected"]), rtol=1e-5, atol=1e-5)
+
+
+def test_plain_rmsnorm_matches_attention_dump_stage():
+    d = golden("dump_attention_block.npz")
+    x = _t(d["input"]).reshape(40, 256)
+    torch.testing.assert_close(og.plain_rmsnorm(x, _t(d["block_norm_w"])).reshape(-1), _t(d["normed"]),
+                               rtol=1e-6, atol=1e-6)
+
+
 def test_norms_match_mamba_dump_stages():
     d = golden("dump_mamba_block.npz")
     x = _t(d["input"]).reshape(24, 64)

@@ -49,9 +49,9 @@ def test_quantizer_edge_cases(ops):
 
 
 def test_quantizer_matches_reference_kernels(ops):
-    path = os.path.join(ROOT, "oracle", "_ref", "libref_mlp_stock.so")
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_blocks_stock.so")
     if not os.path.exists(path):
-        pytest.skip("oracle/_ref/libref_mlp_stock.so not built")
+        pytest.skip("oracle/_ref/libref_blocks_stock.so not built")
     R = ctypes.CDLL(path)
     R.blk_set_device(torch.cuda.current_device())
     x = (3 * torch.randn(4096, 3136, generator=torch.Generator().manual_seed(1))).to(BF).cuda()
