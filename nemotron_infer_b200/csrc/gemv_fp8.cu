@@ -24,6 +24,7 @@ namespace nmt {
 NMT_DEFINE_TIMEOUT_READER();
 
 constexpr int kGemvWarps = 8;
+constexpr int kDefaultGemvVariant = 3;    // 4 = shared-memory ring, 3 = register streaming, 1 / 2 = CUDA-core kernels
 
 // 4 e4m3 bytes (one 32-bit word) -> 4 floats, as two (lo, hi) pairs.
 __device__ __forceinline__ void e4m3x4_to_f32(uint32_t wd, float2& a, float2& b) {
@@ -549,7 +550,7 @@ __host__ __device__ constexpr int ring_row_stride(int K) { return K + ((K % 128)
 template <int SPLIT, int S>
 __global__ void __launch_bounds__(kRingThreads, 2)
 gemv_w8a16_ring_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, const float* __restrict__ w_scale,
-                       __nv_bfloat16* __restrict__ y, int N, int K, int stages, int early_trigger, GemvFusion fu) {
+                       __nv_bfloat16* __restrict__ y, int N, int K, int stages, int early_trigger, int poll, GemvFusion fu) {
     constexpr int R = 16 / S;
     constexpr int TILES = kGemvWarps / SPLIT;
     constexpr int ROWS = R * TILES;                                // matrix rows per stage
@@ -585,7 +586,8 @@ gemv_w8a16_ring_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __res
             bool ok = true;
             for (int n = 0; n < mine && ok; ++n) {
                 const int s = n % stages;
-                if (n >= stages) ok = mbar_wait(&s_empty[s], static_cast<uint32_t>(n / stages - 1) & 1u);
+                if (n >= stages) ok = poll ? mbar_wait_poll(&s_empty[s], static_cast<uint32_t>(n / stages - 1) & 1u)
+                                           : mbar_wait(&s_empty[s], static_cast<uint32_t>(n / stages - 1) & 1u);
                 if (!ok) break;
                 const int64_t row0 = ((int64_t)blockIdx.x + (int64_t)n * gridDim.x) * ROWS;
                 const int rows = static_cast<int>(min((int64_t)ROWS, (int64_t)N - row0));
@@ -701,7 +703,8 @@ gemv_w8a16_ring_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __res
             const int s = n % stages;
             if (waiting) {
                 if (*reinterpret_cast<volatile int*>(&s_abort) != 0) waiting = false;
-                else if (!mbar_wait(&s_full[s], static_cast<uint32_t>(n / stages) & 1u)) { waiting = false; atomicExch(&s_abort, 1); }
+                else if (!(poll ? mbar_wait_poll(&s_full[s], static_cast<uint32_t>(n / stages) & 1u)
+                                : mbar_wait(&s_full[s], static_cast<uint32_t>(n / stages) & 1u))) { waiting = false; atomicExch(&s_abort, 1); }
             }
             const uint8_t* st = ring + (size_t)s * stage_stride;
             float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};    // two chains, so an MMA does not wait for the one before it
@@ -777,7 +780,7 @@ static int launch_gemv_ring(const void* x, const void* W, const float* w_scale, 
         configured[dev] = true;
     }
     launch_kernel(kern, grid, kRingThreads, smem, st, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(W), w_scale,
-                  static_cast<__nv_bfloat16*>(y), N, K, stages, tune("gemv.early_trigger", 1) == 1, fu);
+                  static_cast<__nv_bfloat16*>(y), N, K, stages, tune("gemv.early_trigger", 1) == 1, tune("gemv.ring_poll", 2) == 1, fu);
     return finish_launch(1);
 }
 
@@ -843,7 +846,7 @@ int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, con
     fu.residual = static_cast<const uint16_t*>(residual_bf16);
     // The prologue keeps a thread's share of x in 8 registers-vectors; the fused forms exist only on the tensor-core kernel.
     if (norm_w && (fu.norm_threads > kGemvWarps * 32 || (K / 8 + fu.norm_threads - 1) / fu.norm_threads > 8)) return NMT_ERR_UNSUPPORTED;
-    if (tune("gemv.variant", 4) == 4) {          // 4 = shared-memory ring (default), 3 = register streaming
+    if (tune("gemv.variant", kDefaultGemvVariant) == 4) {
         const int r = launch_gemv_ring_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
                                             static_cast<cudaStream_t>(stream));
         if (r != NMT_ERR_UNSUPPORTED) return r;
@@ -862,7 +865,7 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
     if (K > 45000) return NMT_ERR_UNSUPPORTED;                        // x must fit shared memory as fp32
     const int kv = static_cast<int>(K / 16);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const int variant = tune("gemv.variant", 4); // 4 = shared-memory ring (default), 3 = register streaming, 1 / 2 = CUDA-core kernels
+    const int variant = tune("gemv.variant", kDefaultGemvVariant);
     if (variant == 4) {
         const int r = launch_gemv_ring_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), GemvFusion{}, st);
         if (r != NMT_ERR_UNSUPPORTED) return r;

@@ -56,6 +56,23 @@ __device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity
     return false;
 }
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_limited(bar, parity, kSpinLimit); }
+// The same wait as a plain poll (mbarrier.test_wait returns at once, no suspension): for waiters that expect the phase
+// to complete within a microsecond or so and must not lose that long to a suspended thread's wake-up.  Bounded too.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_poll(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < (1u << 26); ++i)          // ~50 ns per poll: a few seconds at most
+        if (mbar_test_wait(bar, parity)) return true;
+    atomicAdd(&g_wait_timeouts, 1u);
+    return false;
+}
 
 // global -> shared bulk copy; completion (byte count) is signalled on `bar`.
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {

@@ -85,8 +85,10 @@ def run_mamba_bf16(lib, g, x=None, S=None, conv_state=None, ssm_state=None):
     x = g["input"].to(BF) if x is None else x
     S = x.numel() // 64 if S is None else S
     out = torch.empty(S, 64, dtype=BF, device="cuda")
-    rc = lib.blk_mamba_forward_bf16(p(x), p(g["block_norm_w"]), p(g["in_proj_w"].to(BF)), p(g["conv1d_w"]), p(g["conv1d_b"]),
-                                    p(g["A_log"]), p(g["D"]), p(g["dt_bias"]), p(g["gnorm_w"]), p(g["out_proj_w"].to(BF)),
+    in_proj, out_proj = g["in_proj_w"].to(BF), g["out_proj_w"].to(BF)      # named: p() keeps an address, not the tensor
+    rc = lib.blk_mamba_forward_bf16(p(x), p(g["block_norm_w"]), p(in_proj), p(g["conv1d_w"]), p(g["conv1d_b"]),
+                                    p(g["A_log"]), p(g["D"]), p(g["dt_bias"]), p(g["gnorm_w"]), p(out_proj),
                                     p(out), 1, S, p(conv_state), p(ssm_state))
+    torch.cuda.synchronize()
     assert rc == 0
     return out

@@ -21,13 +21,16 @@ _MODS = {}
 
 
 def load_binding(kind):
-    """kind: 'stock' | 'b200'.  Both files define a module called `binding`; each is loaded from its own path."""
+    """kind: 'stock' | 'b200'.  The drop-in is a module called `binding`, like the reference's; the stock build was given
+    the module name `binding_stock` at compile time, because pybind11 keeps one module per name in a process."""
     if kind in _MODS:
         return _MODS[kind]
-    path = os.path.join(ROOT, "oracle", "_ref", f"binding_{kind}", "binding.so")
+    name = "binding" if kind == "b200" else "binding_stock"
+    path = os.path.join(ROOT, "oracle", "_ref", "binding_b200", "binding.so") if kind == "b200" else \
+        os.path.join(ROOT, "oracle", "_ref", "binding_stock.so")
     if not os.path.exists(path):
         pytest.skip(f"{path} not built (needs the reference checkout at build time: make -C oracle binding)")
-    spec = importlib.util.spec_from_file_location("binding", path)
+    spec = importlib.util.spec_from_file_location(name, path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     _MODS[kind] = mod
@@ -41,6 +44,7 @@ def test_module_offers_the_reference_surface(kind):
         assert callable(getattr(m, name)), name
     for name, value in CONSTANTS.items():
         assert getattr(m, name) == value, name
+    assert load_binding("stock") is not load_binding("b200")
 
 
 def _ptr(t):
