@@ -6,9 +6,9 @@
 //
 // Kernels, in the order of the file: two CUDA-core kernels (the general fallback: any K that is a multiple of 16, exact
 // fp32 products for every x; "gemv.variant" = 1 / 2), the register-streaming tensor-core kernel
-// (gemv_w8a16_mma_kernel, "gemv.variant" = 3: K % 64 == 0, any K that fits shared memory as f16) and the default,
-// gemv_w8a16_ring_kernel ("gemv.variant" = 4: K % 64 == 0, K <= 16384), which feeds the same MMA fragments from a
-// shared-memory ring filled by bulk copies.  Common to all:
+// (gemv_w8a16_mma_kernel, "gemv.variant" = 3: K % 64 == 0, f16 MMA after converting the weights) and the default,
+// gemv_w8a16_q8_kernel ("gemv.variant" = 4: K % 64 == 0), which feeds the weight bytes to the e4m3 MMA unconverted
+// and splits x into two e4m3 terms instead.  Common to all:
 //   * Persistent grid.  x is converted once per CTA into shared memory.
 //   * A work unit is (rows, K-slice): rows are cut into slices of a few KB so that short-and-wide matrices
 //     (down_proj: 3136 rows of 12544) still give every warp several units; the warps that share a row sit
@@ -17,14 +17,12 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 
-#include "nmt_tma.cuh"
+#include "nmt_common.cuh"
 
 namespace nmt {
 
-NMT_DEFINE_TIMEOUT_READER();
-
 constexpr int kGemvWarps = 8;
-constexpr int kDefaultGemvVariant = 3;    // 4 = shared-memory ring, 3 = register streaming, 1 / 2 = CUDA-core kernels
+constexpr int kDefaultGemvVariant = 4;    // 4 = e4m3 MMA (x split into two e4m3 terms), 3 = f16 MMA, 1 / 2 = CUDA-core kernels
 
 // 4 e4m3 bytes (one 32-bit word) -> 4 floats, as two (lo, hi) pairs.
 __device__ __forceinline__ void e4m3x4_to_f32(uint32_t wd, float2& a, float2& b) {
@@ -524,278 +522,292 @@ static int launch_gemv_mma_auto(const void* x, const void* W, const float* w_sca
 }
 
 // ---------------------------------------------------------------------------------------------
-// Shared-memory ring.  The register-streaming kernel above keeps its bytes in flight in registers (two load groups of
-// four 16-byte vectors for two A-rows: 64 registers), which caps it at 16 warps per SM and ~50 KB in flight per SM;
-// it runs at 3.6-4.0 TB/s on the model's matrices.  Here the weight stream never touches a register before it is
-// used: consecutive matrix rows are one contiguous range of W, so a STAGE (128 / Q rows, 16-32 KB) is brought in by a
-// single producer lane with cp.async.bulk (one copy per stage, or one per row where rows need a 64-byte skew in
-// shared memory to stay bank-conflict free), completing on the stage's mbarrier; the eight consumer warps take a
-// stage from shared memory with the same permuted-k MMA fragments, 16 bytes per lane per A-row, and hand it back
-// through a second mbarrier.  The ring is full from the kernel's first cycle - before x is staged and before the
-// wait on the preceding kernel - and the last copies are issued long before the last stage is consumed, so the
-// dependent launch can be triggered early.  Every wait is bounded (nmt_tma.cuh); a wait that runs out is counted,
-// the CTA stops waiting, finishes its loop on whatever is in shared memory (its results are void) and the producer
-// drains the copies it has in flight before the CTA leaves.
+// FP8 tensor-core inner product (default).  The f16 kernel above still spends most of its instructions turning
+// weights into f16: two bytes per convert plus the moves that feed it, ~90 warp instructions per KB of W, which at
+// 16 warps per SM is what bounds it (ncu: issue-latency-bound at ~4 TB/s), not HBM.  mma.sync.m16n8k32 takes e4m3
+// operands directly, so here the weight bytes go from the load straight into the MMA: per 64-k chunk and lane two
+// 16-byte loads (its two A-rows), one 16-byte shared-memory read of x and two MMAs - no convert, no unpack.
 //
-// Geometry: Q = S * SPLIT slices per row as above; a warp tile is R = 16 / S rows, a stage TILES = 8 / SPLIT warp
-// tiles, i.e. 128 / Q rows.  Q is chosen so that a slice is 2-4 chunks, which makes a stage 16-32 KB for every K.
+// The activation side pays for it: x is bf16 (8 significant bits), an e4m3 holds 4.  x is therefore scaled by a power
+// of two taken from max|x| (maximum lands in [128, 256)) and split EXACTLY into two e4m3 terms,
+//     x * 2^-e = hi + lo / 16,   hi = x with its low 4 significant bits cleared,   lo = 16 * (x - hi),
+// each of which is one MMA against the same weight registers (two accumulators); the two partial sums are
+// recombined in fp32 as C_hi + C_lo / 16.  Every product e4m3 x e4m3 is exact and accumulation is fp32, as
+// the reference specifies.  The split is exact for every element within 2^-13 of the largest (down to e4m3's
+// smallest normal numbers); smaller elements keep an absolute precision of 2^-18 of the largest element, i.e. they
+// are rounded where the f16 kernel (exact within 2^-28, "gemv.variant" = 3) and the CUDA-core kernels (exact,
+// "gemv.variant" = 1) are not.
+// Everything else - slices, tiles, double-buffered predicated load groups issued before the dependency wait,
+// partial sums parked in shared memory and combined in a fixed order, the fused prologue and epilogues - is the f16
+// kernel's.
 // ---------------------------------------------------------------------------------------------
-constexpr int kRingMaxStages = 8;
-constexpr int kRingThreads = (kGemvWarps + 1) * 32;               // eight consumer warps and the producer warp
+__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Two fp32 values (exactly representable, or to be rounded to nearest) -> two e4m3 bytes, `lo` in the low byte.
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
+    uint32_t r;
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; cvt.u32.u16 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// Shared memory for x as e4m3: the hi plane (K bytes), the lo plane (K bytes), then one chunk of zeros.
+__host__ __device__ constexpr size_t q8_x_bytes(int K) { return (size_t)K * 2 + 64; }
 
-__device__ __forceinline__ void consumer_barrier() { asm volatile("bar.sync 1, %0;" ::"n"(kGemvWarps * 32) : "memory"); }
-
-__host__ __device__ constexpr int ring_row_stride(int K) { return K + ((K % 128) == 0 ? 64 : 0); }
-
-template <int SPLIT, int S>
-__global__ void __launch_bounds__(kRingThreads, 2)
-gemv_w8a16_ring_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, const float* __restrict__ w_scale,
-                       __nv_bfloat16* __restrict__ y, int N, int K, int stages, int early_trigger, int poll, GemvFusion fu) {
+template <int SPLIT, int S>           // S k-streams per tile, R = 16 / S matrix rows per tile
+__global__ void __launch_bounds__(kGemvWarps * 32, 2)
+gemv_w8a16_q8_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, const float* __restrict__ w_scale,
+                     __nv_bfloat16* __restrict__ y, int N, int K, int iters, int early_trigger, GemvFusion fu) {
     constexpr int R = 16 / S;
-    constexpr int TILES = kGemvWarps / SPLIT;
-    constexpr int ROWS = R * TILES;                                // matrix rows per stage
+    constexpr int TILES_PER_CTA = kGemvWarps / SPLIT;
     constexpr int Q = S * SPLIT;                                   // k-slices per matrix row
-    constexpr int NC = kGemvWarps * 32;                            // consumer threads
-    extern __shared__ __align__(128) uint8_t smem_b[];
-    __shared__ uint64_t s_full[kRingMaxStages], s_empty[kRingMaxStages];
+    constexpr int G = kMmaGroup;                                   // chunks per load group
+    extern __shared__ __align__(16) uint8_t smem_b[];
+    uint8_t* xq = smem_b;                                          // [hi plane | lo plane | 64 zero bytes]
+    float* part = reinterpret_cast<float*>(smem_b + q8_x_bytes(K));                    // [iters][warp][16]
     __shared__ float s_red[kGemvWarps];
-    __shared__ float s_part[2][kGemvWarps][16];
-    __shared__ int s_abort;
-    const int Kp = ring_row_stride(K);
-    const size_t stage_stride = (size_t)ROWS * Kp;
-    uint8_t* ring = smem_b;
-    __half* xh = reinterpret_cast<__half*>(smem_b + (size_t)stages * stage_stride);     // K halves, then 64 halves of zero
-    uint32_t* xn = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(xh) + mma_x_bytes(K));   // K bf16: the normalised x
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nstages_total = (N + ROWS - 1) / ROWS;
-    const int mine = nstages_total > (int)blockIdx.x ? (nstages_total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-    int issued = 0;                                                // producer lane: fills whose copies have been issued
+    const int g = lane >> 2, t = lane & 3;
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < stages; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_empty[s], kGemvWarps); }
-        s_abort = 0;
-        mbar_init_fence();
-    }
-    __syncthreads();
+    // ---- this warp's slice geometry (as in the f16 kernel) ----
+    const int kc = K / 64;
+    const int base = kc / Q, rem = kc % Q;
+    auto slice_start = [&](int q) { return q * base + max(0, q - (Q - rem)); };
+    auto slice_len = [&](int q) { return base + (q >= Q - rem ? 1 : 0); };
+    const int split_id = warp % SPLIT, tile_in_cta = warp / SPLIT;
+    const int sA = g / R, rA = g % R, sB = (g + 8) / R, rB = (g + 8) % R;
+    const int cA0 = slice_start(split_id * S + sA), cB0 = slice_start(split_id * S + sB);
+    // x fragment: lanes with g < S feed column g of B with stream g's k range (of the hi plane, then of the lo plane)
+    const int cX0 = g < S ? slice_start(split_id * S + g) : 0, nX = g < S ? slice_len(split_id * S + g) : 0;
+    const int nmax = base + (rem ? 1 : 0);
+    const int groups = (nmax + G - 1) / G;
+    const int ntiles = (N + R - 1) / R;
+    const uint8_t* xzero = xq + 2 * (size_t)K;                     // 64 bytes of zero
+    const uint8_t* xbase = xq + (size_t)cX0 * 64 + t * 16;       // hi plane; the lo plane is K bytes further
+    const size_t offA = (size_t)cA0 * 64 + t * 16, offB = (size_t)cB0 * 64 + t * 16;
 
-    if (warp == kGemvWarps) {
-        // ---------------- producer: one lane keeps the ring full ----------------
-        // The weights are constants of the model, not an output of the preceding kernel: their copies go out without
-        // waiting for that kernel.
-        if (lane == 0) {
-            bool ok = true;
-            for (int n = 0; n < mine && ok; ++n) {
-                const int s = n % stages;
-                if (n >= stages) ok = poll ? mbar_wait_poll(&s_empty[s], static_cast<uint32_t>(n / stages - 1) & 1u)
-                                           : mbar_wait(&s_empty[s], static_cast<uint32_t>(n / stages - 1) & 1u);
-                if (!ok) break;
-                const int64_t row0 = ((int64_t)blockIdx.x + (int64_t)n * gridDim.x) * ROWS;
-                const int rows = static_cast<int>(min((int64_t)ROWS, (int64_t)N - row0));
-                uint8_t* dst = ring + (size_t)s * stage_stride;
-                const uint8_t* src = W + (size_t)row0 * K;
-                mbar_arrive_expect_tx(&s_full[s], static_cast<uint32_t>(rows) * static_cast<uint32_t>(K));
-                if (Kp == K) {
-                    bulk_load(dst, src, static_cast<uint32_t>(rows) * static_cast<uint32_t>(K), &s_full[s]);
-                } else {
-                    for (int r = 0; r < rows; ++r) bulk_load(dst + (size_t)r * Kp, src + (size_t)r * K, static_cast<uint32_t>(K), &s_full[s]);
-                }
-                issued = n + 1;
-            }
-            if (early_trigger) pdl_trigger();                      // every copy of this CTA has been issued
-            if (!ok) atomicExch(&s_abort, 1);                      // counted by mbar_wait; the consumers stop waiting too
+    auto load_group = [&](uint4 (&wa)[G], uint4 (&wb)[G], int it, int grp) {
+        const int tile = (it * gridDim.x + blockIdx.x) * TILES_PER_CTA + tile_in_cta;
+        const bool live = it < iters && tile < ntiles;             // warp-uniform
+        const int j0 = grp * G;
+        const int tl = min(tile, ntiles - 1);
+        const uint8_t* pa = W + (size_t)min(tl * R + rA, N - 1) * K + offA + j0 * 64;
+        const uint8_t* pb = W + (size_t)min(tl * R + rB, N - 1) * K + offB + j0 * 64;
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            const bool on = live && j0 + j < nmax;
+            ld_stream_if(wa[j], pa + j * 64, on);
+            ld_stream_if(wb[j], pb + j * 64, on);
         }
-    } else {
-        // ---------------- consumers ----------------
-        const int g = lane >> 2, t = lane & 3;
-        const int kc = K / 64;
-        const int base = kc / Q, rem = kc % Q;
-        auto slice_start = [&](int q) { return q * base + max(0, q - (Q - rem)); };
-        auto slice_len = [&](int q) { return base + (q >= Q - rem ? 1 : 0); };
-        const int split_id = warp % SPLIT, tile_in_cta = warp / SPLIT;
-        const int sA = g / R, rA = g % R, sB = (g + 8) / R, rB = (g + 8) % R;
-        const int cA0 = slice_start(split_id * S + sA), cB0 = slice_start(split_id * S + sB);
-        const int cX0 = g < S ? slice_start(split_id * S + g) : 0, nX = g < S ? slice_len(split_id * S + g) : 0;
-        const int nmax = base + (rem ? 1 : 0);
-        const __half* xzero = xh + K;
-        const __half* xbase = xh + (size_t)cX0 * 64 + t * 16;
-        const size_t offA = (size_t)(tile_in_cta * R + rA) * Kp + (size_t)cA0 * 64 + t * 16;
-        const size_t offB = (size_t)(tile_in_cta * R + rB) * Kp + (size_t)cB0 * 64 + t * 16;
-
-        pdl_wait();                                                // x (and the residual) may come from the preceding kernel
-
-        // ---- stage x: (optional RMSNorm) -> max|x| -> power-of-two scale -> f16; the ring fills meanwhile ----
-        const uint32_t* xw = reinterpret_cast<const uint32_t*>(x);
-        const int words = K / 2;
-        const bool normed = fu.norm_w != nullptr;                  // block-uniform
-        if (normed) {
-            // The stand-alone kernel's shape (rmsnorm_ctarow_kernel, one row): norm_threads threads, thread t owns
-            // vectors t, t + norm_threads, ...; per-thread f32x2 sums, warp shuffle, then the warps in order.
-            const int nt = fu.norm_threads, nv = K / 8;
-            const uint4* xv = reinterpret_cast<const uint4*>(x);
-            uint4 a[8];
-            if (threadIdx.x < nt) {
-                float2 acc = make_float2(0.f, 0.f);
+    };
+    float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};    // accumulators of the hi and of the lo plane
+    auto compute_group = [&](const uint4 (&wa)[G], const uint4 (&wb)[G], int it, int grp) {
+        const int tile = (it * gridDim.x + blockIdx.x) * TILES_PER_CTA + tile_in_cta;
+        if (it >= iters) return;                                   // warp-uniform
+        if (tile < ntiles) {
+            const int j0 = grp * G;
+            if (grp == 0) c[0] = c[1] = c[2] = c[3] = d[0] = d[1] = d[2] = d[3] = 0.f;
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const int v = q * nt + threadIdx.x;
-                    a[q] = v < nv ? ld_stream(xv + v) : make_uint4(0, 0, 0, 0);
+            for (int j = 0; j < G; ++j) {
+                if (j0 + j < nmax) {                               // warp-uniform
+                    // k of MMA m, register pair (a0, a2) <-> bytes [8m, 8m + 4) and [8m + 4, 8m + 8) of the lane's 16:
+                    // the same permutation of k on the weight side and on the x side
+                    const bool on = j0 + j < nX;
+                    const uint4 xh = *reinterpret_cast<const uint4*>(on ? xbase + (j0 + j) * 64 : xzero);
+                    const uint4 xl = *reinterpret_cast<const uint4*>(on ? xbase + K + (j0 + j) * 64 : xzero);
+                    mma_e4m3(c, wa[j].x, wb[j].x, wa[j].y, wb[j].y, xh.x, xh.y);
+                    mma_e4m3(d, wa[j].x, wb[j].x, wa[j].y, wb[j].y, xl.x, xl.y);
+                    mma_e4m3(c, wa[j].z, wb[j].z, wa[j].w, wb[j].w, xh.z, xh.w);
+                    mma_e4m3(d, wa[j].z, wb[j].z, wa[j].w, wb[j].w, xl.z, xl.w);
                 }
+            }
+        }
+        if (grp == groups - 1) {
+            // C[a][n] is wanted for n = stream(a) only: lane (g, t) holds columns 2t, 2t+1 of A-rows g and g+8
+            float* pw = part + ((size_t)it * kGemvWarps + warp) * 16;
+            if (sA / 2 == t) pw[g] = c[sA & 1] + d[sA & 1] * 0.0625f;
+            if (sB / 2 == t) pw[g + 8] = c[2 + (sB & 1)] + d[2 + (sB & 1)] * 0.0625f;
+        }
+    };
+
+    // The weights are constants of the model, not an output of the preceding kernel: their first loads go out
+    // before the wait on that kernel, and before x is staged, so the stream is already running when x is ready.
+    uint4 wa0[G] = {}, wb0[G] = {}, wa1[G] = {}, wb1[G] = {};
+    load_group(wa0, wb0, 0, 0);
+    pdl_wait();
+
+    // ---- stage x: (optional RMSNorm) -> max|x| -> power-of-two scale -> hi / lo e4m3 planes ----
+    constexpr int XW = 32;                                         // words (bf16 pairs) per thread held in registers
+    const uint32_t* xw = reinterpret_cast<const uint32_t*>(x);
+    const int words = K / 2;
+    const bool held = words <= XW * kGemvWarps * 32;               // block-uniform
+    const bool normed = fu.norm_w != nullptr;                      // block-uniform
+    uint32_t* xn = reinterpret_cast<uint32_t*>(part + (size_t)iters * kGemvWarps * 16);   // K bf16: the normalised x
+    if (normed) {
+        // The stand-alone kernel's shape (rmsnorm_ctarow_kernel, one row): norm_threads threads, thread t owns
+        // vectors t, t + norm_threads, ...; per-thread f32x2 sums, warp shuffle, then the warps in order.
+        const int nt = fu.norm_threads, nv = K / 8;
+        const uint4* xv = reinterpret_cast<const uint4*>(x);
+        uint4 a[8];
+        if (threadIdx.x < nt) {
+            float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
-                for (int q = 0; q < 8; ++q) {
+            for (int q = 0; q < 8; ++q) {
+                const int v = q * nt + threadIdx.x;
+                a[q] = v < nv ? ld_stream(xv + v) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                float2 pr[4];
+                unpack8x2(a[q], pr);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc = __ffma2_rn(pr[k], pr[k], acc);
+            }
+            const float ss = warp_sum(acc.x + acc.y);
+            if (lane == 0) s_red[warp] = ss;
+        }
+        __syncthreads();
+        if (threadIdx.x < nt) {
+            float total = 0.f;
+            for (int i = 0; i < nt / 32; ++i) total += s_red[i];
+            const float rstd = rsqrtf(total * fu.inv_cols + fu.eps);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const int v = q * nt + threadIdx.x;
+                if (v < nv) {
                     float2 pr[4];
                     unpack8x2(a[q], pr);
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) acc = __ffma2_rn(pr[k], pr[k], acc);
-                }
-                const float ss = warp_sum(acc.x + acc.y);
-                if (lane == 0) s_red[warp] = ss;
-            }
-            consumer_barrier();
-            if (threadIdx.x < nt) {
-                float total = 0.f;
-                for (int i = 0; i < nt / 32; ++i) total += s_red[i];
-                const float rstd = rsqrtf(total * fu.inv_cols + fu.eps);
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const int v = q * nt + threadIdx.x;
-                    if (v < nv) {
-                        float2 pr[4];
-                        unpack8x2(a[q], pr);
-                        reinterpret_cast<uint4*>(xn)[v] = scale8(pr, rstd, ld_weight4(fu.norm_w + (size_t)v * 8), ld_weight4(fu.norm_w + (size_t)v * 8 + 4));
-                    }
+                    reinterpret_cast<uint4*>(xn)[v] = scale8(pr, rstd, ld_weight4(fu.norm_w + (size_t)v * 8), ld_weight4(fu.norm_w + (size_t)v * 8 + 4));
                 }
             }
-            consumer_barrier();
         }
-        constexpr int XW = 32;                                     // words (bf16 pairs) per thread held in registers: K <= 16384
-        uint32_t xr[XW];
-        float m = 0.f;
+        __syncthreads();
+    }
+    uint32_t xr[XW];
+    float m = 0.f;
+    if (held) {
 #pragma unroll
         for (int i = 0; i < XW; ++i) {
-            const int idx = threadIdx.x + i * NC;
+            const int idx = threadIdx.x + i * kGemvWarps * 32;
             xr[i] = idx < words ? (normed ? xn[idx] : __ldg(xw + idx)) : 0u;
         }
 #pragma unroll
         for (int i = 0; i < XW; ++i) m = fmaxf(m, fmaxf(fabsf(bf16_lo(xr[i])), fabsf(bf16_hi(xr[i]))));
-        m = warp_max(m);
-        if (lane == 0) s_red[warp] = m;
-        consumer_barrier();
-        float mm = 0.f;
+    } else {
+        for (int i = threadIdx.x; i < words; i += blockDim.x) {
+            const uint32_t u = normed ? xn[i] : xw[i];
+            m = fmaxf(m, fmaxf(fabsf(bf16_lo(u)), fabsf(bf16_hi(u))));
+        }
+    }
+    m = warp_max(m);
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    float mm = 0.f;
 #pragma unroll
-        for (int i = 0; i < kGemvWarps; ++i) mm = fmaxf(mm, s_red[i]);
-        int e = 0;
-        if (mm > 0.f && mm < 3.0e38f) e = static_cast<int>((__float_as_uint(mm) >> 23) & 0xff) - 127 - 14;   // max|x| lands in [2^14, 2^15)
-        e = max(e, -100);                                          // keeps 2^-e and 2^e normal fp32 numbers
-        const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);      // 2^-e
-        const float up = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);        // 2^e
+    for (int i = 0; i < kGemvWarps; ++i) mm = fmaxf(mm, s_red[i]);
+    int e = 0;
+    if (mm > 0.f && mm < 3.0e38f) e = static_cast<int>((__float_as_uint(mm) >> 23) & 0xff) - 127 - 7;   // max|x| lands in [2^7, 2^8)
+    e = max(e, -120);                                              // keeps 2^-e and 2^e normal fp32 numbers
+    const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);      // 2^-e
+    // One bf16 pair -> (hi, hi) and (lo, lo) e4m3 pairs.  A bf16 is 1.7 bits; clearing the low four mantissa bits leaves
+    // the four significant bits an e4m3 holds, and the remainder times 16 has at most four significant bits as well.
+    auto split_store = [&](int idx, uint32_t u) {
+        const float x0 = bf16_lo(u) * down, x1 = bf16_hi(u) * down;
+        const float h0 = __uint_as_float(__float_as_uint(x0) & 0xfff00000u), h1 = __uint_as_float(__float_as_uint(x1) & 0xfff00000u);
+        reinterpret_cast<uint16_t*>(xq)[idx] = static_cast<uint16_t>(f32x2_to_e4m3x2(h0, h1));
+        reinterpret_cast<uint16_t*>(xq + K)[idx] = static_cast<uint16_t>(f32x2_to_e4m3x2((x0 - h0) * 16.f, (x1 - h1) * 16.f));
+    };
+    if (held) {
 #pragma unroll
         for (int i = 0; i < XW; ++i) {
-            const int idx = threadIdx.x + i * NC;
-            if (idx < words) reinterpret_cast<__half2*>(xh)[idx] = __floats2half2_rn(bf16_lo(xr[i]) * down, bf16_hi(xr[i]) * down);
+            const int idx = threadIdx.x + i * kGemvWarps * 32;
+            if (idx < words) split_store(idx, xr[i]);
         }
-        if (threadIdx.x < 32) reinterpret_cast<uint32_t*>(xh + K)[threadIdx.x] = 0u;
-        consumer_barrier();
+    } else {
+        for (int i = threadIdx.x; i < words; i += blockDim.x) split_store(i, normed ? xn[i] : xw[i]);
+    }
+    if (threadIdx.x < 16) reinterpret_cast<uint32_t*>(xq + 2 * (size_t)K)[threadIdx.x] = 0u;
+    __syncthreads();
 
-        // ---- consume the ring ----
-        bool waiting = true;                                       // false once a wait has run out anywhere in the CTA
+    // ---- stream: the next group's loads are in flight while this group is multiplied ----
+    int cit = 0, cgrp = 0, lit = 0, lgrp = 0;                      // (work unit, group) being computed / loaded
+    auto step = [&](int& it, int& grp) { if (++grp == groups) { grp = 0; ++it; } };
+    step(lit, lgrp);
 #pragma unroll 1
-        for (int n = 0; n < mine; ++n) {
-            const int s = n % stages;
-            if (waiting) {
-                if (*reinterpret_cast<volatile int*>(&s_abort) != 0) waiting = false;
-                else if (!(poll ? mbar_wait_poll(&s_full[s], static_cast<uint32_t>(n / stages) & 1u)
-                                : mbar_wait(&s_full[s], static_cast<uint32_t>(n / stages) & 1u))) { waiting = false; atomicExch(&s_abort, 1); }
-            }
-            const uint8_t* st = ring + (size_t)s * stage_stride;
-            float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};    // two chains, so an MMA does not wait for the one before it
-#pragma unroll 4
-            for (int j = 0; j < nmax; ++j) {
-                const uint4 wa = lds128(st + offA + (size_t)j * 64);
-                const uint4 wb = lds128(st + offB + (size_t)j * 64);
-                const uint4* xp = reinterpret_cast<const uint4*>(j < nX ? xbase + j * 64 : xzero);
-                const uint4 x0 = xp[0], x1 = xp[1];
-                const uint32_t wa_[4] = {wa.x, wa.y, wa.z, wa.w};
-                const uint32_t wb_[4] = {wb.x, wb.y, wb.z, wb.w};
-                const uint32_t xb_[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                    mma_f16((q & 1) ? d : c, e4m3_lo(wa_[q]), e4m3_lo(wb_[q]), e4m3_hi(wa_[q]), e4m3_hi(wb_[q]), xb_[2 * q], xb_[2 * q + 1]);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[s]);               // this warp is done with the stage's bytes
-            // C[a][n] is wanted for n = stream(a) only: lane (g, t) holds columns 2t, 2t+1 of A-rows g and g+8
-            float* pw = s_part[n & 1][warp];
-            if (sA / 2 == t) pw[g] = c[sA & 1] + d[sA & 1];
-            if (sB / 2 == t) pw[g + 8] = c[2 + (sB & 1)] + d[2 + (sB & 1)];
-            consumer_barrier();
-            // matrix row r of warp tile tc = sum over the split warps and streams, in a fixed order
-            if (threadIdx.x < ROWS) {
-                const int tc = threadIdx.x / R, r = threadIdx.x % R;
-                const int64_t row = ((int64_t)blockIdx.x + (int64_t)n * gridDim.x) * ROWS + threadIdx.x;
-                if (row < N) {
-                    float sum = 0.f;
-#pragma unroll
-                    for (int sp = 0; sp < SPLIT; ++sp)
-#pragma unroll
-                        for (int s2 = 0; s2 < S; ++s2) sum += s_part[n & 1][tc * SPLIT + sp][s2 * R + r];
-                    // bf16 result in the low half of a pair, so the epilogues can use the stand-alone kernels' instructions
-                    uint32_t yb = pack_bf16x2((sum * up) * __ldg(w_scale + row), 0.f);
-                    if (fu.activation == 1) yb = relu2_bf16x2(yb);
-                    if (fu.residual) yb = add_bf16x2_rn(static_cast<uint32_t>(fu.residual[row]), yb);
-                    reinterpret_cast<uint16_t*>(y)[row] = static_cast<uint16_t>(yb & 0xffffu);
-                }
-            }
-        }
+    while (cit < iters) {
+        load_group(wa1, wb1, lit, lgrp);
+        step(lit, lgrp);
+        compute_group(wa0, wb0, cit, cgrp);
+        step(cit, cgrp);
+        load_group(wa0, wb0, lit, lgrp);
+        step(lit, lgrp);
+        if (early_trigger && lit >= iters) pdl_trigger();          // every load of this warp has been issued
+        compute_group(wa1, wb1, cit, cgrp);
+        step(cit, cgrp);
     }
     __syncthreads();
-    // A wait ran out somewhere in this CTA (counted; its results are void): the consumers may have gone through the
-    // ring without waiting, so copies may still be in flight.  The producer lane does not leave - and the CTA's shared
-    // memory is not released - before the last fill of every stage has landed (bounded waits again).
-    if (warp == kGemvWarps && lane == 0 && *reinterpret_cast<volatile int*>(&s_abort) != 0) {
-        for (int n = max(0, issued - stages); n < issued; ++n)
-            mbar_wait(&s_full[n % stages], static_cast<uint32_t>(n / stages) & 1u);
+    // ---- combine: matrix row r of tile T = sum over streams s and split warps of part[..][s*R + r] ----
+    const float up = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);         // 2^e
+    for (int o = threadIdx.x; o < iters * TILES_PER_CTA * R; o += blockDim.x) {
+        const int it = o / (TILES_PER_CTA * R), rest = o % (TILES_PER_CTA * R);
+        const int tc = rest / R, r = rest % R;
+        const int row = ((it * gridDim.x + blockIdx.x) * TILES_PER_CTA + tc) * R + r;
+        if (row < N) {
+            float sum = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < SPLIT; ++sp)
+#pragma unroll
+                for (int s2 = 0; s2 < S; ++s2) sum += part[((size_t)it * kGemvWarps + tc * SPLIT + sp) * 16 + s2 * R + r];
+            // bf16 result in the low half of a pair, so the epilogues can use the stand-alone kernels' instructions
+            uint32_t yb = pack_bf16x2((sum * up) * __ldg(w_scale + row), 0.f);
+            if (fu.activation == 1) yb = relu2_bf16x2(yb);
+            if (fu.residual) yb = add_bf16x2_rn(static_cast<uint32_t>(fu.residual[row]), yb);
+            reinterpret_cast<uint16_t*>(y)[row] = static_cast<uint16_t>(yb & 0xffffu);
+        }
     }
-    pdl_trigger();
+    if (!early_trigger) pdl_trigger();
 }
 
 template <int SPLIT, int S>
-static int launch_gemv_ring(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
-    constexpr int R = 16 / S, TILES = kGemvWarps / SPLIT, ROWS = R * TILES;
-    auto kern = gemv_w8a16_ring_kernel<SPLIT, S>;
-    const size_t stage_stride = (size_t)ROWS * ring_row_stride(K);
-    const size_t fixed = mma_x_bytes(K) + (fu.norm_w ? (size_t)K * 2 : 0);
-    int stages = tune("gemv.ring_stages", 3);         // 3 leaves room for the next launch's CTA beside this one
-    if (stages > kRingMaxStages) stages = kRingMaxStages;
-    while (stages > 2 && stages * stage_stride + fixed > 200 * 1024) --stages;
-    const size_t smem = stages * stage_stride + fixed;
-    if (stages < 2 || smem > 200 * 1024) return NMT_ERR_UNSUPPORTED;
-    const int nstages_total = (N + ROWS - 1) / ROWS;
-    const int per_sm = tune("gemv.ctas_per_sm", 1) >= 2 && 2 * smem <= 220 * 1024 ? 2 : 1;   // two only where both fit an SM
-    const int grid = nstages_total < kSmCount * per_sm ? nstages_total : kSmCount * per_sm;
+static int launch_gemv_q8(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
+    constexpr int R = 16 / S, TILES_PER_CTA = kGemvWarps / SPLIT;
+    auto kern = gemv_w8a16_q8_kernel<SPLIT, S>;
+    const int ntiles = (N + R - 1) / R;
+    const int ctas_needed = (ntiles + TILES_PER_CTA - 1) / TILES_PER_CTA;
+    const int per_sm = tune("gemv.ctas_per_sm", 2);
+    int iters = (ctas_needed + kSmCount * per_sm - 1) / (kSmCount * per_sm);      // passes per CTA ...
+    if (iters < 1) iters = 1;
+    const int grid = (ctas_needed + iters - 1) / iters;                           // ... evenly spread over the grid
+    const size_t smem = q8_x_bytes(K) + (size_t)iters * kGemvWarps * 16 * sizeof(float) + (fu.norm_w ? (size_t)K * 2 : 0);
+    if (smem > 200 * 1024) return NMT_ERR_UNSUPPORTED;
     static bool configured[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
+    if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !configured[dev]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return finish_launch(0);
         configured[dev] = true;
     }
-    launch_kernel(kern, grid, kRingThreads, smem, st, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(W), w_scale,
-                  static_cast<__nv_bfloat16*>(y), N, K, stages, tune("gemv.early_trigger", 1) == 1, tune("gemv.ring_poll", 2) == 1, fu);
+    launch_kernel(kern, grid, kGemvWarps * 32, smem, st, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(W),
+                  w_scale, static_cast<__nv_bfloat16*>(y), N, K, iters, tune("gemv.early_trigger", 1) == 1, fu);
     return finish_launch(1);
 }
 
-// Slices per row so that a slice is 2-4 chunks (a stage 16-32 KB); all eight warps share one warp tile when the row
-// is long enough.  NMT_ERR_UNSUPPORTED when x does not fit the register staging (K > 16384) or K % 64 != 0.
-static int launch_gemv_ring_auto(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
-    if ((K % 64) != 0 || K > 16384) return NMT_ERR_UNSUPPORTED;
+// Slices per row so that a work unit is about six chunks (as for the f16 kernel).
+static int launch_gemv_q8_auto(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
+    if ((K % 64) != 0) return NMT_ERR_UNSUPPORTED;
     const int kc = K / 64;
     int q = 1;
-    while (q < 64 && (kc + q - 1) / q > tune("gemv.unit_chunks", 4)) q *= 2;
-    const int split = q >= 8 ? 8 : q, streams = q / split;
-#define NMT_RING_CASE(SP, ST) if (split == SP && streams == ST) return launch_gemv_ring<SP, ST>(x, W, w_scale, y, N, K, fu, st)
-    NMT_RING_CASE(1, 1); NMT_RING_CASE(2, 1); NMT_RING_CASE(4, 1);
-    NMT_RING_CASE(8, 1); NMT_RING_CASE(8, 2); NMT_RING_CASE(8, 4); NMT_RING_CASE(8, 8);
-#undef NMT_RING_CASE
+    while (q < 64 && (kc + q - 1) / q > tune("gemv.unit_chunks", 7)) q *= 2;                                 // slices per row
+    if ((kc + q - 1) / q > kMmaMaxChunks) return NMT_ERR_UNSUPPORTED;
+    const int forced = tune("gemv.streams", 0);
+    int split = q >= 8 ? 8 : q, streams = q / split;
+    if (forced > 0 && forced <= 8 && q % forced == 0 && q / forced <= 8) { streams = forced; split = q / forced; }
+#define NMT_Q8_CASE(SP, ST) if (split == SP && streams == ST) return launch_gemv_q8<SP, ST>(x, W, w_scale, y, N, K, fu, st)
+    NMT_Q8_CASE(1, 1); NMT_Q8_CASE(2, 1); NMT_Q8_CASE(4, 1); NMT_Q8_CASE(8, 1);
+    NMT_Q8_CASE(1, 2); NMT_Q8_CASE(2, 2); NMT_Q8_CASE(4, 2); NMT_Q8_CASE(8, 2);
+    NMT_Q8_CASE(1, 4); NMT_Q8_CASE(2, 4); NMT_Q8_CASE(4, 4); NMT_Q8_CASE(8, 4);
+    NMT_Q8_CASE(1, 8); NMT_Q8_CASE(2, 8); NMT_Q8_CASE(4, 8); NMT_Q8_CASE(8, 8);
+#undef NMT_Q8_CASE
     return NMT_ERR_UNSUPPORTED;
 }
 
@@ -847,8 +859,8 @@ int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, con
     // The prologue keeps a thread's share of x in 8 registers-vectors; the fused forms exist only on the tensor-core kernel.
     if (norm_w && (fu.norm_threads > kGemvWarps * 32 || (K / 8 + fu.norm_threads - 1) / fu.norm_threads > 8)) return NMT_ERR_UNSUPPORTED;
     if (tune("gemv.variant", kDefaultGemvVariant) == 4) {
-        const int r = launch_gemv_ring_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
-                                            static_cast<cudaStream_t>(stream));
+        const int r = launch_gemv_q8_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
+                                          static_cast<cudaStream_t>(stream));
         if (r != NMT_ERR_UNSUPPORTED) return r;
     }
     return launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
@@ -867,7 +879,7 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int variant = tune("gemv.variant", kDefaultGemvVariant);
     if (variant == 4) {
-        const int r = launch_gemv_ring_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), GemvFusion{}, st);
+        const int r = launch_gemv_q8_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), GemvFusion{}, st);
         if (r != NMT_ERR_UNSUPPORTED) return r;
     }
     if (variant >= 3) {

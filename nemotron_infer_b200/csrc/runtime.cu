@@ -38,13 +38,11 @@ static Knob g_knobs[] = {
     {"conv.pairs", {0}},          // causal conv1d: channel pairs per thread (2 = 8-byte vectors, 4 = 16-byte vectors)
     {"conv.unroll", {0}},         // causal conv1d: loads issued ahead of use (4 or 8)
     {"gemv.split", {0}},          // W8A16 GEMV: K-slices per row (1, 2, 4, 8); 0 = by K
-    {"gemv.variant", {0}},        // W8A16 GEMV: 4 = mma.sync fed from a shared-memory ring of bulk copies (default), 3 = mma.sync fed from registers, 1 = whole-unit CUDA-core loads, 2 = looped loads
-    {"gemv.ring_poll", {0}},      // W8A16 GEMV (ring): 1 = waits poll mbarrier.test_wait, 2 (default) = mbarrier.try_wait with a suspend hint
-    {"gemv.ring_stages", {0}},    // W8A16 GEMV (ring): stages of 16-32 KB per CTA, 2..8 (default 3)
+    {"gemv.variant", {0}},        // W8A16 GEMV: 4 = e4m3 MMA on the raw weight bytes, x as two e4m3 terms (default), 3 = f16 MMA, 1 = whole-unit CUDA-core loads, 2 = looped loads
     {"gemv.early_trigger", {0}},  // W8A16 GEMV (mma): 1 (default) = let the next kernel launch once this one's last loads are issued, 2 = at the very end
-    {"gemv.unit_chunks", {0}},    // W8A16 GEMV (mma): largest number of 64-k chunks per k-slice (default 4 for the ring, 7 for the register kernel)
+    {"gemv.unit_chunks", {0}},    // W8A16 GEMV (mma): largest number of 64-k chunks per work unit (default 7)
     {"gemv.streams", {0}},        // W8A16 GEMV (mma): k-streams per 16-row tile (1, 2, 4, 8); 0 = by shape
-    {"gemv.ctas_per_sm", {0}},    // W8A16 GEMV: persistent CTAs per SM; 0 = by shared-memory footprint (ring: 1)
+    {"gemv.ctas_per_sm", {0}},    // W8A16 GEMV: persistent CTAs per SM; 0 = by shared-memory footprint
     // gated rmsnorm (bf16)
     {"gated.block", {0}},
     {"gated.ctas_per_sm", {0}},

@@ -89,6 +89,34 @@ def test_tensor_core_path_positions_and_codes(ops):
         assert torch.equal(got, want), K
 
 
+def test_default_kernel_splits_x_exactly_within_thirteen_binades_of_its_maximum(ops):
+    """The default kernel multiplies e4m3 weights with x split into two e4m3 terms after scaling max|x| into [128, 256).
+    One-hot weight rows read single elements of x back: every element within 2^-12 of the largest must come back
+    exactly (all 8 significant bits of the bf16), smaller ones with an absolute error of at most 2^-17 of the largest;
+    the f16 kernel (variant 3) and the fp32-product kernel (variant 1) return all of them exactly."""
+    K = 64 * 18
+    mant = 1 + (torch.arange(K) % 128).float() / 128                      # every 8-bit significand
+    expo = -(torch.arange(K) // 64).float()                               # 2^0 ... 2^-17, 64 elements each
+    x = (mant * torch.pow(torch.tensor(2.0), expo)).to(BF)
+    x[0] = 1.9921875                                                      # the maximum: 1.1111111b
+    W = torch.zeros(K, K)
+    W[torch.arange(K), torch.arange(K)] = 1.0
+    Wq, sc = W.to(torch.float8_e4m3fn), torch.ones(K)
+    want = x.float()
+    try:
+        for variant in (4, 3, 1):
+            ops.tune("gemv.variant", variant)
+            got = ops.gemv_w8a16(x.cuda(), Wq.cuda(), sc.cuda()).float().cpu()
+            if variant == 4:
+                exact = expo >= -12
+                assert torch.equal(got[exact], want[exact])
+                assert float((got - want).abs().max()) <= 2.0 ** -17 * 1.9921875
+            else:
+                assert torch.equal(got, want), variant
+    finally:
+        ops.tune("gemv.variant", 0)
+
+
 @pytest.mark.parametrize("scale", [1e30, 1e-30, 3e4, 2.0 ** -20])
 def test_tensor_core_path_x_magnitudes(ops, scale):
     """x is staged as f16 times a power of two taken from max|x|: huge and tiny vectors must come out as accurately
@@ -105,7 +133,7 @@ def test_tensor_core_path_x_magnitudes(ops, scale):
 
 @pytest.mark.parametrize("N,K", [(40, 64), (9, 192), (300, 16384), (50, 16448), (1000, 512), (17, 32704), (5000, 3136),
                                  (1237, 12544), (333, 7680), (148 * 8 + 1, 128)])
-def test_tensor_core_path_slicing(ops, built_lib, N, K):
+def test_tensor_core_path_slicing(ops, N, K):
     """Shapes that exercise one chunk per row, uneven slices, the register-held and re-read x staging, many
     k-streams per tile and ragged last tiles; every stream count the knob allows."""
     g = torch.Generator().manual_seed(N * 7 + K)
@@ -113,25 +141,16 @@ def test_tensor_core_path_slicing(ops, built_lib, N, K):
     W, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
     want = og.gemv_w8a16(x, W, sc)
     try:
-        ops.tune("gemv.variant", 3)                  # the register-streaming kernel
-        for streams in (0, 1, 2, 4, 8):
-            for chunks in (0, 2, 4):
-                ops.tune("gemv.streams", streams)
-                ops.tune("gemv.unit_chunks", chunks)
-                check(ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()), want)
-        ops.tune("gemv.streams", 0)
-        ops.tune("gemv.variant", 4)                  # the shared-memory ring (default where K <= 16384)
-        for stages in (0, 2, 4, 8):
-            for chunks in (0, 2, 3, 7):
-                for per_sm in (0, 2):
-                    ops.tune("gemv.ring_stages", stages)
+        for variant in (4, 3):                       # 4 = e4m3 MMA (default), 3 = f16 MMA
+            ops.tune("gemv.variant", variant)
+            for streams in (0, 1, 2, 4, 8):
+                for chunks in (0, 2, 4):
+                    ops.tune("gemv.streams", streams)
                     ops.tune("gemv.unit_chunks", chunks)
-                    ops.tune("gemv.ctas_per_sm", per_sm)
                     check(ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()), want)
     finally:
-        for k in ("gemv.streams", "gemv.unit_chunks", "gemv.variant", "gemv.ring_stages", "gemv.ctas_per_sm"):
+        for k in ("gemv.streams", "gemv.unit_chunks", "gemv.variant"):
             ops.tune(k, 0)
-    assert built_lib.nmt_device_wait_timeouts() == 0
 
 
 @pytest.mark.parametrize("N,K", [(12544, 3136), (3136, 12544), (17504, 3136), (3136, 7680), (40, 64), (16, 10240)])
