@@ -257,6 +257,117 @@ struct GemvFusion {
     const uint16_t* residual;     // non-null: y += residual[row]
 };
 
+// Two fp32 values (exactly representable, or to be rounded to nearest) -> two e4m3 bytes, `lo` in the low byte.
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
+    uint32_t r;
+    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; cvt.u32.u16 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// ---------------------------------------------------------------------------------------------
+// Staging of x, shared by the two tensor-core kernels.  Every CTA needs all of x in shared memory in the MMA's operand
+// format, and (fused form) normalises its own copy first.  This runs once per CTA and sits between the kernel's start
+// and its first MMA, so its length is a fixed cost of every launch: the loops below are bounded by K (8 bf16 per
+// thread and step, 16-byte accesses) - an earlier version walked a fully unrolled 32-slot register array whatever K
+// was and spent ~900 warp instructions per warp on a 3136-wide x, a third of the kernel's instruction stream.
+//   1. optional RMSNorm in the stand-alone kernel's shape (rmsnorm_ctarow_kernel, one row): norm_threads threads,
+//      thread t owns vectors t, t + norm_threads, ...; per-thread f32x2 sums, warp shuffle, then the warps in order -
+//      the normalised bf16 row lands in `xn` (shared memory) and equals the stand-alone kernel's output bit for bit;
+//   2. max|x| -> exponent e so that max|x| * 2^-e lies in [2^top, 2^(top+1));
+//   3. x * 2^-e -> operand format: f16 (kernel 3) or the two e4m3 planes hi | lo (kernel 4), plus one chunk of zeros.
+// Returns e.  Ends with a block barrier; all kGemvWarps * 32 threads must call it.
+// ---------------------------------------------------------------------------------------------
+// One bf16 pair -> (hi, hi) and (lo, lo) e4m3 pairs.  A bf16 has 8 significant bits; clearing the low four mantissa bits
+// leaves the four an e4m3 holds, and 16 times the remainder has at most four significant bits as well.
+__device__ __forceinline__ void split_pair(uint32_t u, float down, uint32_t& hi2, uint32_t& lo2) {
+    const float x0 = bf16_lo(u) * down, x1 = bf16_hi(u) * down;
+    const float h0 = __uint_as_float(__float_as_uint(x0) & 0xfff00000u), h1 = __uint_as_float(__float_as_uint(x1) & 0xfff00000u);
+    hi2 = f32x2_to_e4m3x2(h0, h1);
+    lo2 = f32x2_to_e4m3x2((x0 - h0) * 16.f, (x1 - h1) * 16.f);
+}
+
+template <bool Q8>
+__device__ __forceinline__ int stage_x(const __nv_bfloat16* __restrict__ x, const GemvFusion& fu, int K, uint8_t* xs, uint4* xn,
+                                       float* s_red) {
+    constexpr int NT = kGemvWarps * 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nv = K / 8;                                          // 16-byte vectors of x
+    const uint4* xv = reinterpret_cast<const uint4*>(x);
+    const bool normed = fu.norm_w != nullptr;                      // block-uniform
+    if (normed) {
+        const int nt = fu.norm_threads;
+        if (threadIdx.x < nt) {
+            float2 acc = make_float2(0.f, 0.f);
+#pragma unroll 2
+            for (int v = threadIdx.x; v < nv; v += nt) {
+                float2 pr[4];
+                unpack8x2(ld_stream(xv + v), pr);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) acc = __ffma2_rn(pr[k], pr[k], acc);
+            }
+            const float ss = warp_sum(acc.x + acc.y);
+            if (lane == 0) s_red[warp] = ss;
+        }
+        __syncthreads();
+        if (threadIdx.x < nt) {
+            float total = 0.f;
+            for (int i = 0; i < nt / 32; ++i) total += s_red[i];
+            const float rstd = rsqrtf(total * fu.inv_cols + fu.eps);
+#pragma unroll 2
+            for (int v = threadIdx.x; v < nv; v += nt) {
+                float2 pr[4];
+                unpack8x2(ld_stream(xv + v), pr);                  // second read of a row that sits in L1 / L2
+                xn[v] = scale8(pr, rstd, ld_weight4(fu.norm_w + (size_t)v * 8), ld_weight4(fu.norm_w + (size_t)v * 8 + 4));
+            }
+        }
+        __syncthreads();
+    }
+    const uint4* src = normed ? xn : xv;
+    float m = 0.f;
+#pragma unroll 2
+    for (int v = threadIdx.x; v < nv; v += NT) {
+        const uint4 u = normed ? src[v] : __ldg(src + v);
+        const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) m = fmaxf(m, fmaxf(fabsf(bf16_lo(w4[k])), fabsf(bf16_hi(w4[k]))));
+    }
+    m = warp_max(m);
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    float mm = 0.f;
+#pragma unroll
+    for (int i = 0; i < kGemvWarps; ++i) mm = fmaxf(mm, s_red[i]);
+    constexpr int top = Q8 ? 7 : 14;                               // e4m3: max below 448; f16: max below 65504
+    int e = 0;
+    if (mm > 0.f && mm < 3.0e38f) e = static_cast<int>((__float_as_uint(mm) >> 23) & 0xff) - 127 - top;
+    e = max(e, Q8 ? -120 : -100);                                  // keeps 2^-e and 2^e normal fp32 numbers
+    const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);      // 2^-e
+#pragma unroll 2
+    for (int v = threadIdx.x; v < nv; v += NT) {
+        const uint4 u = normed ? src[v] : __ldg(src + v);
+        const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+        if (Q8) {
+            uint32_t h[4], l[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) split_pair(w4[k], down, h[k], l[k]);
+            *reinterpret_cast<uint2*>(xs + (size_t)v * 8) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+            *reinterpret_cast<uint2*>(xs + (size_t)K + (size_t)v * 8) = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+        } else {
+            uint32_t hw[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                __half2 h2 = __floats2half2_rn(bf16_lo(w4[k]) * down, bf16_hi(w4[k]) * down);
+                hw[k] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            *reinterpret_cast<uint4*>(xs + (size_t)v * 16) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        }
+    }
+    // one chunk of zeros behind x: what lanes with nothing to contribute multiply with
+    uint8_t* zero = xs + (size_t)K * 2;
+    if (threadIdx.x < (Q8 ? 16 : 32)) reinterpret_cast<uint32_t*>(zero)[threadIdx.x] = 0u;
+    __syncthreads();
+    return e;
+}
+
 template <int SPLIT, int S>           // S k-streams per tile, R = 16 / S matrix rows per tile
 __global__ void __launch_bounds__(kGemvWarps * 32)
 gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, const float* __restrict__ w_scale,
@@ -287,7 +398,6 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __rest
     const int cX0 = g < S ? slice_start(split_id * S + g) : 0, nX = g < S ? slice_len(split_id * S + g) : 0;
     const int nmax = base + (rem ? 1 : 0);
     const int groups = (nmax + G - 1) / G;                         // load groups per work unit
-    const int total = iters * groups;                              // load groups of this warp, in order
     const int ntiles = (N + R - 1) / R;
 
     // Ragged edges are handled on the x side so that no weight register ever needs a zero fill: a row past N is read
@@ -338,122 +448,37 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __rest
         if (grp == groups - 1) {
             // C[a][n] is wanted for n = stream(a) only: lane (g, t) holds columns 2t, 2t+1 of A-rows g and g+8
             float* pw = part + ((size_t)it * kGemvWarps + warp) * 16;
-            if (sA / 2 == t) pw[g] = c[sA & 1] + d[sA & 1];
-            if (sB / 2 == t) pw[g + 8] = c[2 + (sB & 1)] + d[2 + (sB & 1)];
+            if (sA / 2 == t) pw[g] = (sA & 1) ? c[1] + d[1] : c[0] + d[0];
+            if (sB / 2 == t) pw[g + 8] = (sB & 1) ? c[3] + d[3] : c[2] + d[2];
         }
     };
 
-    // The weights are constants of the model, not an output of the preceding kernel: their first loads go out
+    // The weights are constants of the model, not an output of the preceding kernel: the first two load groups go out
     // before the wait on that kernel, and before x is staged, so the stream is already running when x is ready.
     uint4 wa0[G] = {}, wb0[G] = {}, wa1[G] = {}, wb1[G] = {};
-    load_group(wa0, wb0, 0, 0);
-    pdl_wait();
-
-    // ---- stage x: max|x| -> power-of-two scale -> f16 ----
-    // x is read once and kept in registers between the two steps when it fits (K <= 16384); every load is issued
-    // before the first use, so staging costs one trip to L2 plus two barriers.
-    constexpr int XW = 32;                                         // words (bf16 pairs) per thread held in registers
-    const uint32_t* xw = reinterpret_cast<const uint32_t*>(x);
-    const int words = K / 2;
-    const bool held = words <= XW * kGemvWarps * 32;               // block-uniform
-    const bool normed = fu.norm_w != nullptr;                      // block-uniform
-    uint32_t* xn = reinterpret_cast<uint32_t*>(part + (size_t)iters * kGemvWarps * 16);   // K bf16: the normalised x
-    if (normed) {
-        // The stand-alone kernel's shape (rmsnorm_ctarow_kernel, one row): norm_threads threads, thread t owns
-        // vectors t, t + norm_threads, ...; per-thread f32x2 sums, warp shuffle, then the warps in order.
-        const int nt = fu.norm_threads, nv = K / 8;
-        const uint4* xv = reinterpret_cast<const uint4*>(x);
-        uint4 a[8];
-        if (threadIdx.x < nt) {
-            float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int v = q * nt + threadIdx.x;
-                a[q] = v < nv ? ld_stream(xv + v) : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                float2 pr[4];
-                unpack8x2(a[q], pr);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) acc = __ffma2_rn(pr[k], pr[k], acc);
-            }
-            const float ss = warp_sum(acc.x + acc.y);
-            if (lane == 0) s_red[warp] = ss;
-        }
-        __syncthreads();
-        if (threadIdx.x < nt) {
-            float total = 0.f;
-            for (int i = 0; i < nt / 32; ++i) total += s_red[i];
-            const float rstd = rsqrtf(total * fu.inv_cols + fu.eps);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int v = q * nt + threadIdx.x;
-                if (v < nv) {
-                    float2 pr[4];
-                    unpack8x2(a[q], pr);
-                    reinterpret_cast<uint4*>(xn)[v] = scale8(pr, rstd, ld_weight4(fu.norm_w + (size_t)v * 8), ld_weight4(fu.norm_w + (size_t)v * 8 + 4));
-                }
-            }
-        }
-        __syncthreads();
-    }
-    uint32_t xr[XW];
-    float m = 0.f;
-    if (held) {
-#pragma unroll
-        for (int i = 0; i < XW; ++i) {
-            const int idx = threadIdx.x + i * kGemvWarps * 32;
-            xr[i] = idx < words ? (normed ? xn[idx] : __ldg(xw + idx)) : 0u;
-        }
-#pragma unroll
-        for (int i = 0; i < XW; ++i) m = fmaxf(m, fmaxf(fabsf(bf16_lo(xr[i])), fabsf(bf16_hi(xr[i]))));
-    } else {
-        for (int i = threadIdx.x; i < words; i += blockDim.x) {
-            const uint32_t u = normed ? xn[i] : xw[i];
-            m = fmaxf(m, fmaxf(fabsf(bf16_lo(u)), fabsf(bf16_hi(u))));
-        }
-    }
-    m = warp_max(m);
-    if (lane == 0) s_red[warp] = m;
-    __syncthreads();
-    float mm = 0.f;
-#pragma unroll
-    for (int i = 0; i < kGemvWarps; ++i) mm = fmaxf(mm, s_red[i]);
-    int e = 0;
-    if (mm > 0.f && mm < 3.0e38f) e = static_cast<int>((__float_as_uint(mm) >> 23) & 0xff) - 127 - 14;   // max|x| lands in [2^14, 2^15)
-    e = max(e, -100);                                              // keeps 2^-e and 2^e normal fp32 numbers
-    const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);      // 2^-e
-    if (held) {
-#pragma unroll
-        for (int i = 0; i < XW; ++i) {
-            const int idx = threadIdx.x + i * kGemvWarps * 32;
-            if (idx < words) reinterpret_cast<__half2*>(xh)[idx] = __floats2half2_rn(bf16_lo(xr[i]) * down, bf16_hi(xr[i]) * down);
-        }
-    } else {
-        for (int i = threadIdx.x; i < words; i += blockDim.x) {
-            const uint32_t u = normed ? xn[i] : xw[i];
-            reinterpret_cast<__half2*>(xh)[i] = __floats2half2_rn(bf16_lo(u) * down, bf16_hi(u) * down);
-        }
-    }
-    if (threadIdx.x < 32) reinterpret_cast<uint32_t*>(xh + K)[threadIdx.x] = 0u;
-    __syncthreads();
-
-    // ---- stream: the next group's loads are in flight while this group is multiplied ----
     int cit = 0, cgrp = 0, lit = 0, lgrp = 0;                      // (work unit, group) being computed / loaded
     auto step = [&](int& it, int& grp) { if (++grp == groups) { grp = 0; ++it; } };
+    load_group(wa0, wb0, lit, lgrp);
     step(lit, lgrp);
+    load_group(wa1, wb1, lit, lgrp);
+    step(lit, lgrp);
+    pdl_wait();
+
+    uint4* xn = reinterpret_cast<uint4*>(part + (size_t)iters * kGemvWarps * 16);        // K bf16: the normalised x
+    const int e = stage_x<false>(x, fu, K, reinterpret_cast<uint8_t*>(xh), xn, s_red);
+
+    // ---- stream: the next groups' loads are in flight while this group is multiplied ----
 #pragma unroll 1
     while (cit < iters) {
-        load_group(wa1, wb1, lit, lgrp);
-        step(lit, lgrp);
         compute_group(wa0, wb0, cit, cgrp);
         step(cit, cgrp);
         load_group(wa0, wb0, lit, lgrp);
         step(lit, lgrp);
-        if (early_trigger && lit >= iters) pdl_trigger();          // every load of this warp has been issued
         compute_group(wa1, wb1, cit, cgrp);
         step(cit, cgrp);
+        load_group(wa1, wb1, lit, lgrp);
+        step(lit, lgrp);
+        if (early_trigger && lit >= iters) pdl_trigger();          // every load of this warp has been issued
     }
     __syncthreads();
     // ---- combine: matrix row r of tile T = sum over streams s and split warps of part[..][s*R + r] ----
@@ -545,12 +570,6 @@ __device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1
     asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// Two fp32 values (exactly representable, or to be rounded to nearest) -> two e4m3 bytes, `lo` in the low byte.
-__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
-    uint32_t r;
-    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; cvt.u32.u16 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
 // Shared memory for x as e4m3: the hi plane (K bytes), the lo plane (K bytes), then one chunk of zeros.
 __host__ __device__ constexpr size_t q8_x_bytes(int K) { return (size_t)K * 2 + 64; }
 
@@ -625,125 +644,37 @@ gemv_w8a16_q8_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restr
         if (grp == groups - 1) {
             // C[a][n] is wanted for n = stream(a) only: lane (g, t) holds columns 2t, 2t+1 of A-rows g and g+8
             float* pw = part + ((size_t)it * kGemvWarps + warp) * 16;
-            if (sA / 2 == t) pw[g] = c[sA & 1] + d[sA & 1] * 0.0625f;
-            if (sB / 2 == t) pw[g + 8] = c[2 + (sB & 1)] + d[2 + (sB & 1)] * 0.0625f;
+            if (sA / 2 == t) pw[g] = (sA & 1) ? c[1] + d[1] * 0.0625f : c[0] + d[0] * 0.0625f;
+            if (sB / 2 == t) pw[g + 8] = (sB & 1) ? c[3] + d[3] * 0.0625f : c[2] + d[2] * 0.0625f;
         }
     };
 
-    // The weights are constants of the model, not an output of the preceding kernel: their first loads go out
+    // The weights are constants of the model, not an output of the preceding kernel: the first two load groups go out
     // before the wait on that kernel, and before x is staged, so the stream is already running when x is ready.
     uint4 wa0[G] = {}, wb0[G] = {}, wa1[G] = {}, wb1[G] = {};
-    load_group(wa0, wb0, 0, 0);
-    pdl_wait();
-
-    // ---- stage x: (optional RMSNorm) -> max|x| -> power-of-two scale -> hi / lo e4m3 planes ----
-    constexpr int XW = 32;                                         // words (bf16 pairs) per thread held in registers
-    const uint32_t* xw = reinterpret_cast<const uint32_t*>(x);
-    const int words = K / 2;
-    const bool held = words <= XW * kGemvWarps * 32;               // block-uniform
-    const bool normed = fu.norm_w != nullptr;                      // block-uniform
-    uint32_t* xn = reinterpret_cast<uint32_t*>(part + (size_t)iters * kGemvWarps * 16);   // K bf16: the normalised x
-    if (normed) {
-        // The stand-alone kernel's shape (rmsnorm_ctarow_kernel, one row): norm_threads threads, thread t owns
-        // vectors t, t + norm_threads, ...; per-thread f32x2 sums, warp shuffle, then the warps in order.
-        const int nt = fu.norm_threads, nv = K / 8;
-        const uint4* xv = reinterpret_cast<const uint4*>(x);
-        uint4 a[8];
-        if (threadIdx.x < nt) {
-            float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int v = q * nt + threadIdx.x;
-                a[q] = v < nv ? ld_stream(xv + v) : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                float2 pr[4];
-                unpack8x2(a[q], pr);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) acc = __ffma2_rn(pr[k], pr[k], acc);
-            }
-            const float ss = warp_sum(acc.x + acc.y);
-            if (lane == 0) s_red[warp] = ss;
-        }
-        __syncthreads();
-        if (threadIdx.x < nt) {
-            float total = 0.f;
-            for (int i = 0; i < nt / 32; ++i) total += s_red[i];
-            const float rstd = rsqrtf(total * fu.inv_cols + fu.eps);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const int v = q * nt + threadIdx.x;
-                if (v < nv) {
-                    float2 pr[4];
-                    unpack8x2(a[q], pr);
-                    reinterpret_cast<uint4*>(xn)[v] = scale8(pr, rstd, ld_weight4(fu.norm_w + (size_t)v * 8), ld_weight4(fu.norm_w + (size_t)v * 8 + 4));
-                }
-            }
-        }
-        __syncthreads();
-    }
-    uint32_t xr[XW];
-    float m = 0.f;
-    if (held) {
-#pragma unroll
-        for (int i = 0; i < XW; ++i) {
-            const int idx = threadIdx.x + i * kGemvWarps * 32;
-            xr[i] = idx < words ? (normed ? xn[idx] : __ldg(xw + idx)) : 0u;
-        }
-#pragma unroll
-        for (int i = 0; i < XW; ++i) m = fmaxf(m, fmaxf(fabsf(bf16_lo(xr[i])), fabsf(bf16_hi(xr[i]))));
-    } else {
-        for (int i = threadIdx.x; i < words; i += blockDim.x) {
-            const uint32_t u = normed ? xn[i] : xw[i];
-            m = fmaxf(m, fmaxf(fabsf(bf16_lo(u)), fabsf(bf16_hi(u))));
-        }
-    }
-    m = warp_max(m);
-    if (lane == 0) s_red[warp] = m;
-    __syncthreads();
-    float mm = 0.f;
-#pragma unroll
-    for (int i = 0; i < kGemvWarps; ++i) mm = fmaxf(mm, s_red[i]);
-    int e = 0;
-    if (mm > 0.f && mm < 3.0e38f) e = static_cast<int>((__float_as_uint(mm) >> 23) & 0xff) - 127 - 7;   // max|x| lands in [2^7, 2^8)
-    e = max(e, -120);                                              // keeps 2^-e and 2^e normal fp32 numbers
-    const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);      // 2^-e
-    // One bf16 pair -> (hi, hi) and (lo, lo) e4m3 pairs.  A bf16 is 1.7 bits; clearing the low four mantissa bits leaves
-    // the four significant bits an e4m3 holds, and the remainder times 16 has at most four significant bits as well.
-    auto split_store = [&](int idx, uint32_t u) {
-        const float x0 = bf16_lo(u) * down, x1 = bf16_hi(u) * down;
-        const float h0 = __uint_as_float(__float_as_uint(x0) & 0xfff00000u), h1 = __uint_as_float(__float_as_uint(x1) & 0xfff00000u);
-        reinterpret_cast<uint16_t*>(xq)[idx] = static_cast<uint16_t>(f32x2_to_e4m3x2(h0, h1));
-        reinterpret_cast<uint16_t*>(xq + K)[idx] = static_cast<uint16_t>(f32x2_to_e4m3x2((x0 - h0) * 16.f, (x1 - h1) * 16.f));
-    };
-    if (held) {
-#pragma unroll
-        for (int i = 0; i < XW; ++i) {
-            const int idx = threadIdx.x + i * kGemvWarps * 32;
-            if (idx < words) split_store(idx, xr[i]);
-        }
-    } else {
-        for (int i = threadIdx.x; i < words; i += blockDim.x) split_store(i, normed ? xn[i] : xw[i]);
-    }
-    if (threadIdx.x < 16) reinterpret_cast<uint32_t*>(xq + 2 * (size_t)K)[threadIdx.x] = 0u;
-    __syncthreads();
-
-    // ---- stream: the next group's loads are in flight while this group is multiplied ----
     int cit = 0, cgrp = 0, lit = 0, lgrp = 0;                      // (work unit, group) being computed / loaded
     auto step = [&](int& it, int& grp) { if (++grp == groups) { grp = 0; ++it; } };
+    load_group(wa0, wb0, lit, lgrp);
     step(lit, lgrp);
+    load_group(wa1, wb1, lit, lgrp);
+    step(lit, lgrp);
+    pdl_wait();
+
+    uint4* xn = reinterpret_cast<uint4*>(part + (size_t)iters * kGemvWarps * 16);        // K bf16: the normalised x
+    const int e = stage_x<true>(x, fu, K, xq, xn, s_red);
+
+    // ---- stream: the next groups' loads are in flight while this group is multiplied ----
 #pragma unroll 1
     while (cit < iters) {
-        load_group(wa1, wb1, lit, lgrp);
-        step(lit, lgrp);
         compute_group(wa0, wb0, cit, cgrp);
         step(cit, cgrp);
         load_group(wa0, wb0, lit, lgrp);
         step(lit, lgrp);
-        if (early_trigger && lit >= iters) pdl_trigger();          // every load of this warp has been issued
         compute_group(wa1, wb1, cit, cgrp);
         step(cit, cgrp);
+        load_group(wa1, wb1, lit, lgrp);
+        step(lit, lgrp);
+        if (early_trigger && lit >= iters) pdl_trigger();          // every load of this warp has been issued
     }
     __syncthreads();
     // ---- combine: matrix row r of tile T = sum over streams s and split warps of part[..][s*R + r] ----
