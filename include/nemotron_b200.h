@@ -207,11 +207,8 @@ int nmt_causal_conv1d_silu_f32(const float* x, const float* w, const float* bias
 /* y[n] = bf16((sum_k e4m3(W[n,k]) * bf16(x[k])) * w_scale[n]), fp32 accumulation.  Replaces
  * nemotron::ops::gemv_fp8 (ops/gemv.cuh:87-104; kernel :48-85), same arguments: W is [N, K] row-major e4m3 with
  * one fp32 scale per output row, x is K bf16 activations.  K % 16 == 0, W 16-byte aligned.
- * When K % 64 == 0 the products run on the e4m3 tensor-core path: the weight bytes are used as they are, and x,
- * scaled by a power of two taken from max|x|, is split into two e4m3 terms whose partial sums are recombined in
- * fp32.  The split is exact for every element within 2^-12 of the largest |x|; smaller elements are rounded with an
- * absolute error of at most 2^-17 * max|x|.  nmt_tune_set("gemv.variant", 3) selects the f16 tensor-core kernel
- * (exact for elements within 2^-28 of the maximum), ("gemv.variant", 1) keeps fp32 products for every element.
+ * When K % 64 == 0 the products run on tensor cores with x held as f16 times a power of two taken from max|x|:
+ * exact for elements within 2^-28 of the maximum (nmt_tune_set("gemv.variant", 1) keeps fp32 products).
  * Ordering contract: W and w_scale are model constants to this kernel -- its first weight loads are issued
  * before it waits for the kernel that precedes it on the stream (programmatic dependent launch), so that
  * preceding kernel must not be the one that writes W or w_scale (an on-the-fly weight quantiser, a staging

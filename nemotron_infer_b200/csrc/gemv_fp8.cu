@@ -6,9 +6,7 @@
 //
 // Kernels, in the order of the file: two CUDA-core kernels (the general fallback: any K that is a multiple of 16, exact
 // fp32 products for every x; "gemv.variant" = 1 / 2), the register-streaming tensor-core kernel
-// (gemv_w8a16_mma_kernel, "gemv.variant" = 3: K % 64 == 0, f16 MMA after converting the weights) and the default,
-// gemv_w8a16_q8_kernel ("gemv.variant" = 4: K % 64 == 0), which feeds the weight bytes to the e4m3 MMA unconverted
-// and splits x into two e4m3 terms instead.  Common to all:
+// (gemv_w8a16_mma_kernel, the default: K % 64 == 0, f16 MMA after converting the weights).  Common to all:
 //   * Persistent grid.  x is converted once per CTA into shared memory.
 //   * A work unit is (rows, K-slice): rows are cut into slices of a few KB so that short-and-wide matrices
 //     (down_proj: 3136 rows of 12544) still give every warp several units; the warps that share a row sit
@@ -22,7 +20,7 @@
 namespace nmt {
 
 constexpr int kGemvWarps = 8;
-constexpr int kDefaultGemvVariant = 4;    // 4 = e4m3 MMA (x split into two e4m3 terms), 3 = f16 MMA, 1 / 2 = CUDA-core kernels
+constexpr int kDefaultGemvVariant = 3;    // 3 = tensor-core inner product, 1 / 2 = CUDA-core kernels
 
 // 4 e4m3 bytes (one 32-bit word) -> 4 floats, as two (lo, hi) pairs.
 __device__ __forceinline__ void e4m3x4_to_f32(uint32_t wd, float2& a, float2& b) {
@@ -257,35 +255,19 @@ struct GemvFusion {
     const uint16_t* residual;     // non-null: y += residual[row]
 };
 
-// Two fp32 values (exactly representable, or to be rounded to nearest) -> two e4m3 bytes, `lo` in the low byte.
-__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi) {
-    uint32_t r;
-    asm("{ .reg .b16 t; cvt.rn.satfinite.e4m3x2.f32 t, %1, %2; cvt.u32.u16 %0, t; }" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
 // ---------------------------------------------------------------------------------------------
-// Staging of x, shared by the two tensor-core kernels.  Every CTA needs all of x in shared memory in the MMA's operand
-// format, and (fused form) normalises its own copy first.  This runs once per CTA and sits between the kernel's start
+// Staging of x.  Every CTA needs all of x in shared memory in the MMA's operand format, and (fused form) normalises
+// its own copy first.  This runs once per CTA and sits between the kernel's start
 // and its first MMA, so its length is a fixed cost of every launch: the loops below are bounded by K (8 bf16 per
 // thread and step, 16-byte accesses) - an earlier version walked a fully unrolled 32-slot register array whatever K
 // was and spent ~900 warp instructions per warp on a 3136-wide x, a third of the kernel's instruction stream.
 //   1. optional RMSNorm in the stand-alone kernel's shape (rmsnorm_ctarow_kernel, one row): norm_threads threads,
 //      thread t owns vectors t, t + norm_threads, ...; per-thread f32x2 sums, warp shuffle, then the warps in order -
 //      the normalised bf16 row lands in `xn` (shared memory) and equals the stand-alone kernel's output bit for bit;
-//   2. max|x| -> exponent e so that max|x| * 2^-e lies in [2^top, 2^(top+1));
-//   3. x * 2^-e -> operand format: f16 (kernel 3) or the two e4m3 planes hi | lo (kernel 4), plus one chunk of zeros.
+//   2. max|x| -> exponent e so that max|x| * 2^-e lies in [2^14, 2^15);
+//   3. x * 2^-e -> f16, plus one chunk of zeros.
 // Returns e.  Ends with a block barrier; all kGemvWarps * 32 threads must call it.
 // ---------------------------------------------------------------------------------------------
-// One bf16 pair -> (hi, hi) and (lo, lo) e4m3 pairs.  A bf16 has 8 significant bits; clearing the low four mantissa bits
-// leaves the four an e4m3 holds, and 16 times the remainder has at most four significant bits as well.
-__device__ __forceinline__ void split_pair(uint32_t u, float down, uint32_t& hi2, uint32_t& lo2) {
-    const float x0 = bf16_lo(u) * down, x1 = bf16_hi(u) * down;
-    const float h0 = __uint_as_float(__float_as_uint(x0) & 0xfff00000u), h1 = __uint_as_float(__float_as_uint(x1) & 0xfff00000u);
-    hi2 = f32x2_to_e4m3x2(h0, h1);
-    lo2 = f32x2_to_e4m3x2((x0 - h0) * 16.f, (x1 - h1) * 16.f);
-}
-
-template <bool Q8>
 __device__ __forceinline__ int stage_x(const __nv_bfloat16* __restrict__ x, const GemvFusion& fu, int K, uint8_t* xs, uint4* xn,
                                        float* s_red) {
     constexpr int NT = kGemvWarps * 32;
@@ -336,34 +318,25 @@ __device__ __forceinline__ int stage_x(const __nv_bfloat16* __restrict__ x, cons
     float mm = 0.f;
 #pragma unroll
     for (int i = 0; i < kGemvWarps; ++i) mm = fmaxf(mm, s_red[i]);
-    constexpr int top = Q8 ? 7 : 14;                               // e4m3: max below 448; f16: max below 65504
     int e = 0;
-    if (mm > 0.f && mm < 3.0e38f) e = static_cast<int>((__float_as_uint(mm) >> 23) & 0xff) - 127 - top;
-    e = max(e, Q8 ? -120 : -100);                                  // keeps 2^-e and 2^e normal fp32 numbers
+    if (mm > 0.f && mm < 3.0e38f) e = static_cast<int>((__float_as_uint(mm) >> 23) & 0xff) - 127 - 14;   // max|x| lands in [2^14, 2^15)
+    e = max(e, -100);                                              // keeps 2^-e and 2^e normal fp32 numbers
     const float down = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);      // 2^-e
 #pragma unroll 2
     for (int v = threadIdx.x; v < nv; v += NT) {
         const uint4 u = normed ? src[v] : __ldg(src + v);
         const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-        if (Q8) {
-            uint32_t h[4], l[4];
+        uint32_t hw[4];
 #pragma unroll
-            for (int k = 0; k < 4; ++k) split_pair(w4[k], down, h[k], l[k]);
-            *reinterpret_cast<uint2*>(xs + (size_t)v * 8) = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
-            *reinterpret_cast<uint2*>(xs + (size_t)K + (size_t)v * 8) = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
-        } else {
-            uint32_t hw[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                __half2 h2 = __floats2half2_rn(bf16_lo(w4[k]) * down, bf16_hi(w4[k]) * down);
-                hw[k] = *reinterpret_cast<uint32_t*>(&h2);
-            }
-            *reinterpret_cast<uint4*>(xs + (size_t)v * 16) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        for (int k = 0; k < 4; ++k) {
+            __half2 h2 = __floats2half2_rn(bf16_lo(w4[k]) * down, bf16_hi(w4[k]) * down);
+            hw[k] = *reinterpret_cast<uint32_t*>(&h2);
         }
+        *reinterpret_cast<uint4*>(xs + (size_t)v * 16) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
     }
     // one chunk of zeros behind x: what lanes with nothing to contribute multiply with
     uint8_t* zero = xs + (size_t)K * 2;
-    if (threadIdx.x < (Q8 ? 16 : 32)) reinterpret_cast<uint32_t*>(zero)[threadIdx.x] = 0u;
+    if (threadIdx.x < 32) reinterpret_cast<uint32_t*>(zero)[threadIdx.x] = 0u;
     __syncthreads();
     return e;
 }
@@ -465,7 +438,7 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __rest
     pdl_wait();
 
     uint4* xn = reinterpret_cast<uint4*>(part + (size_t)iters * kGemvWarps * 16);        // K bf16: the normalised x
-    const int e = stage_x<false>(x, fu, K, reinterpret_cast<uint8_t*>(xh), xn, s_red);
+    const int e = stage_x(x, fu, K, reinterpret_cast<uint8_t*>(xh), xn, s_red);
 
     // ---- stream: the next groups' loads are in flight while this group is multiplied ----
 #pragma unroll 1
@@ -509,10 +482,12 @@ static int launch_gemv_mma(const void* x, const void* W, const float* w_scale, v
     auto kern = gemv_w8a16_mma_kernel<SPLIT, S>;
     const int ntiles = (N + R - 1) / R;
     const int ctas_needed = (ntiles + TILES_PER_CTA - 1) / TILES_PER_CTA;
+    // Every SM gets its full complement of CTAs and the work units go round them (unit u belongs to CTA u % grid), so
+    // that no SM carries more than one unit more than another: with the grid shrunk to ceil(units / passes) some SMs
+    // held two CTAs and some one, and the busiest SM had 13 % more bytes than the average at the model's shapes.
     const int per_sm = tune("gemv.ctas_per_sm", 2);
-    int iters = (ctas_needed + kSmCount * per_sm - 1) / (kSmCount * per_sm);      // passes per CTA ...
-    if (iters < 1) iters = 1;
-    const int grid = (ctas_needed + iters - 1) / iters;                           // ... evenly spread over the grid
+    const int grid = ctas_needed < kSmCount * per_sm ? ctas_needed : kSmCount * per_sm;
+    const int iters = (ctas_needed + grid - 1) / grid;                            // passes of the busiest CTA
     const size_t smem = mma_x_bytes(K) + (size_t)iters * kGemvWarps * 16 * sizeof(float) + (fu.norm_w ? (size_t)K * 2 : 0);
     if (smem > 200 * 1024) return NMT_ERR_UNSUPPORTED;
     static bool configured[64] = {};
@@ -543,202 +518,6 @@ static int launch_gemv_mma_auto(const void* x, const void* W, const float* w_sca
     NMT_MMA_CASE(1, 4); NMT_MMA_CASE(2, 4); NMT_MMA_CASE(4, 4); NMT_MMA_CASE(8, 4);
     NMT_MMA_CASE(1, 8); NMT_MMA_CASE(2, 8); NMT_MMA_CASE(4, 8); NMT_MMA_CASE(8, 8);
 #undef NMT_MMA_CASE
-    return NMT_ERR_UNSUPPORTED;
-}
-
-// ---------------------------------------------------------------------------------------------
-// FP8 tensor-core inner product (default).  The f16 kernel above still spends most of its instructions turning
-// weights into f16: two bytes per convert plus the moves that feed it, ~90 warp instructions per KB of W, which at
-// 16 warps per SM is what bounds it (ncu: issue-latency-bound at ~4 TB/s), not HBM.  mma.sync.m16n8k32 takes e4m3
-// operands directly, so here the weight bytes go from the load straight into the MMA: per 64-k chunk and lane two
-// 16-byte loads (its two A-rows), one 16-byte shared-memory read of x and two MMAs - no convert, no unpack.
-//
-// The activation side pays for it: x is bf16 (8 significant bits), an e4m3 holds 4.  x is therefore scaled by a power
-// of two taken from max|x| (maximum lands in [128, 256)) and split EXACTLY into two e4m3 terms,
-//     x * 2^-e = hi + lo / 16,   hi = x with its low 4 significant bits cleared,   lo = 16 * (x - hi),
-// each of which is one MMA against the same weight registers (two accumulators); the two partial sums are
-// recombined in fp32 as C_hi + C_lo / 16.  Every product e4m3 x e4m3 is exact and accumulation is fp32, as
-// the reference specifies.  The split is exact for every element within 2^-13 of the largest (down to e4m3's
-// smallest normal numbers); smaller elements keep an absolute precision of 2^-18 of the largest element, i.e. they
-// are rounded where the f16 kernel (exact within 2^-28, "gemv.variant" = 3) and the CUDA-core kernels (exact,
-// "gemv.variant" = 1) are not.
-// Everything else - slices, tiles, double-buffered predicated load groups issued before the dependency wait,
-// partial sums parked in shared memory and combined in a fixed order, the fused prologue and epilogues - is the f16
-// kernel's.
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void mma_e4m3(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.f32.e4m3.e4m3.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-// Shared memory for x as e4m3: the hi plane (K bytes), the lo plane (K bytes), then one chunk of zeros.
-__host__ __device__ constexpr size_t q8_x_bytes(int K) { return (size_t)K * 2 + 64; }
-
-template <int SPLIT, int S>           // S k-streams per tile, R = 16 / S matrix rows per tile
-__global__ void __launch_bounds__(kGemvWarps * 32, 2)
-gemv_w8a16_q8_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, const float* __restrict__ w_scale,
-                     __nv_bfloat16* __restrict__ y, int N, int K, int iters, int early_trigger, GemvFusion fu) {
-    constexpr int R = 16 / S;
-    constexpr int TILES_PER_CTA = kGemvWarps / SPLIT;
-    constexpr int Q = S * SPLIT;                                   // k-slices per matrix row
-    constexpr int G = kMmaGroup;                                   // chunks per load group
-    extern __shared__ __align__(16) uint8_t smem_b[];
-    uint8_t* xq = smem_b;                                          // [hi plane | lo plane | 64 zero bytes]
-    float* part = reinterpret_cast<float*>(smem_b + q8_x_bytes(K));                    // [iters][warp][16]
-    __shared__ float s_red[kGemvWarps];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int g = lane >> 2, t = lane & 3;
-
-    // ---- this warp's slice geometry (as in the f16 kernel) ----
-    const int kc = K / 64;
-    const int base = kc / Q, rem = kc % Q;
-    auto slice_start = [&](int q) { return q * base + max(0, q - (Q - rem)); };
-    auto slice_len = [&](int q) { return base + (q >= Q - rem ? 1 : 0); };
-    const int split_id = warp % SPLIT, tile_in_cta = warp / SPLIT;
-    const int sA = g / R, rA = g % R, sB = (g + 8) / R, rB = (g + 8) % R;
-    const int cA0 = slice_start(split_id * S + sA), cB0 = slice_start(split_id * S + sB);
-    // x fragment: lanes with g < S feed column g of B with stream g's k range (of the hi plane, then of the lo plane)
-    const int cX0 = g < S ? slice_start(split_id * S + g) : 0, nX = g < S ? slice_len(split_id * S + g) : 0;
-    const int nmax = base + (rem ? 1 : 0);
-    const int groups = (nmax + G - 1) / G;
-    const int ntiles = (N + R - 1) / R;
-    const uint8_t* xzero = xq + 2 * (size_t)K;                     // 64 bytes of zero
-    const uint8_t* xbase = xq + (size_t)cX0 * 64 + t * 16;       // hi plane; the lo plane is K bytes further
-    const size_t offA = (size_t)cA0 * 64 + t * 16, offB = (size_t)cB0 * 64 + t * 16;
-
-    auto load_group = [&](uint4 (&wa)[G], uint4 (&wb)[G], int it, int grp) {
-        const int tile = (it * gridDim.x + blockIdx.x) * TILES_PER_CTA + tile_in_cta;
-        const bool live = it < iters && tile < ntiles;             // warp-uniform
-        const int j0 = grp * G;
-        const int tl = min(tile, ntiles - 1);
-        const uint8_t* pa = W + (size_t)min(tl * R + rA, N - 1) * K + offA + j0 * 64;
-        const uint8_t* pb = W + (size_t)min(tl * R + rB, N - 1) * K + offB + j0 * 64;
-#pragma unroll
-        for (int j = 0; j < G; ++j) {
-            const bool on = live && j0 + j < nmax;
-            ld_stream_if(wa[j], pa + j * 64, on);
-            ld_stream_if(wb[j], pb + j * 64, on);
-        }
-    };
-    float c[4] = {0.f, 0.f, 0.f, 0.f}, d[4] = {0.f, 0.f, 0.f, 0.f};    // accumulators of the hi and of the lo plane
-    auto compute_group = [&](const uint4 (&wa)[G], const uint4 (&wb)[G], int it, int grp) {
-        const int tile = (it * gridDim.x + blockIdx.x) * TILES_PER_CTA + tile_in_cta;
-        if (it >= iters) return;                                   // warp-uniform
-        if (tile < ntiles) {
-            const int j0 = grp * G;
-            if (grp == 0) c[0] = c[1] = c[2] = c[3] = d[0] = d[1] = d[2] = d[3] = 0.f;
-#pragma unroll
-            for (int j = 0; j < G; ++j) {
-                if (j0 + j < nmax) {                               // warp-uniform
-                    // k of MMA m, register pair (a0, a2) <-> bytes [8m, 8m + 4) and [8m + 4, 8m + 8) of the lane's 16:
-                    // the same permutation of k on the weight side and on the x side
-                    const bool on = j0 + j < nX;
-                    const uint4 xh = *reinterpret_cast<const uint4*>(on ? xbase + (j0 + j) * 64 : xzero);
-                    const uint4 xl = *reinterpret_cast<const uint4*>(on ? xbase + K + (j0 + j) * 64 : xzero);
-                    mma_e4m3(c, wa[j].x, wb[j].x, wa[j].y, wb[j].y, xh.x, xh.y);
-                    mma_e4m3(d, wa[j].x, wb[j].x, wa[j].y, wb[j].y, xl.x, xl.y);
-                    mma_e4m3(c, wa[j].z, wb[j].z, wa[j].w, wb[j].w, xh.z, xh.w);
-                    mma_e4m3(d, wa[j].z, wb[j].z, wa[j].w, wb[j].w, xl.z, xl.w);
-                }
-            }
-        }
-        if (grp == groups - 1) {
-            // C[a][n] is wanted for n = stream(a) only: lane (g, t) holds columns 2t, 2t+1 of A-rows g and g+8
-            float* pw = part + ((size_t)it * kGemvWarps + warp) * 16;
-            if (sA / 2 == t) pw[g] = (sA & 1) ? c[1] + d[1] * 0.0625f : c[0] + d[0] * 0.0625f;
-            if (sB / 2 == t) pw[g + 8] = (sB & 1) ? c[3] + d[3] * 0.0625f : c[2] + d[2] * 0.0625f;
-        }
-    };
-
-    // The weights are constants of the model, not an output of the preceding kernel: the first two load groups go out
-    // before the wait on that kernel, and before x is staged, so the stream is already running when x is ready.
-    uint4 wa0[G] = {}, wb0[G] = {}, wa1[G] = {}, wb1[G] = {};
-    int cit = 0, cgrp = 0, lit = 0, lgrp = 0;                      // (work unit, group) being computed / loaded
-    auto step = [&](int& it, int& grp) { if (++grp == groups) { grp = 0; ++it; } };
-    load_group(wa0, wb0, lit, lgrp);
-    step(lit, lgrp);
-    load_group(wa1, wb1, lit, lgrp);
-    step(lit, lgrp);
-    pdl_wait();
-
-    uint4* xn = reinterpret_cast<uint4*>(part + (size_t)iters * kGemvWarps * 16);        // K bf16: the normalised x
-    const int e = stage_x<true>(x, fu, K, xq, xn, s_red);
-
-    // ---- stream: the next groups' loads are in flight while this group is multiplied ----
-#pragma unroll 1
-    while (cit < iters) {
-        compute_group(wa0, wb0, cit, cgrp);
-        step(cit, cgrp);
-        load_group(wa0, wb0, lit, lgrp);
-        step(lit, lgrp);
-        compute_group(wa1, wb1, cit, cgrp);
-        step(cit, cgrp);
-        load_group(wa1, wb1, lit, lgrp);
-        step(lit, lgrp);
-        if (early_trigger && lit >= iters) pdl_trigger();          // every load of this warp has been issued
-    }
-    __syncthreads();
-    // ---- combine: matrix row r of tile T = sum over streams s and split warps of part[..][s*R + r] ----
-    const float up = __uint_as_float(static_cast<uint32_t>(127 + e) << 23);         // 2^e
-    for (int o = threadIdx.x; o < iters * TILES_PER_CTA * R; o += blockDim.x) {
-        const int it = o / (TILES_PER_CTA * R), rest = o % (TILES_PER_CTA * R);
-        const int tc = rest / R, r = rest % R;
-        const int row = ((it * gridDim.x + blockIdx.x) * TILES_PER_CTA + tc) * R + r;
-        if (row < N) {
-            float sum = 0.f;
-#pragma unroll
-            for (int sp = 0; sp < SPLIT; ++sp)
-#pragma unroll
-                for (int s2 = 0; s2 < S; ++s2) sum += part[((size_t)it * kGemvWarps + tc * SPLIT + sp) * 16 + s2 * R + r];
-            // bf16 result in the low half of a pair, so the epilogues can use the stand-alone kernels' instructions
-            uint32_t yb = pack_bf16x2((sum * up) * __ldg(w_scale + row), 0.f);
-            if (fu.activation == 1) yb = relu2_bf16x2(yb);
-            if (fu.residual) yb = add_bf16x2_rn(static_cast<uint32_t>(fu.residual[row]), yb);
-            reinterpret_cast<uint16_t*>(y)[row] = static_cast<uint16_t>(yb & 0xffffu);
-        }
-    }
-    if (!early_trigger) pdl_trigger();
-}
-
-template <int SPLIT, int S>
-static int launch_gemv_q8(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
-    constexpr int R = 16 / S, TILES_PER_CTA = kGemvWarps / SPLIT;
-    auto kern = gemv_w8a16_q8_kernel<SPLIT, S>;
-    const int ntiles = (N + R - 1) / R;
-    const int ctas_needed = (ntiles + TILES_PER_CTA - 1) / TILES_PER_CTA;
-    const int per_sm = tune("gemv.ctas_per_sm", 2);
-    int iters = (ctas_needed + kSmCount * per_sm - 1) / (kSmCount * per_sm);      // passes per CTA ...
-    if (iters < 1) iters = 1;
-    const int grid = (ctas_needed + iters - 1) / iters;                           // ... evenly spread over the grid
-    const size_t smem = q8_x_bytes(K) + (size_t)iters * kGemvWarps * 16 * sizeof(float) + (fu.norm_w ? (size_t)K * 2 : 0);
-    if (smem > 200 * 1024) return NMT_ERR_UNSUPPORTED;
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (smem > 48 * 1024 && dev >= 0 && dev < 64 && !configured[dev]) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return finish_launch(0);
-        configured[dev] = true;
-    }
-    launch_kernel(kern, grid, kGemvWarps * 32, smem, st, static_cast<const __nv_bfloat16*>(x), static_cast<const uint8_t*>(W),
-                  w_scale, static_cast<__nv_bfloat16*>(y), N, K, iters, tune("gemv.early_trigger", 1) == 1, fu);
-    return finish_launch(1);
-}
-
-// Slices per row so that a work unit is about six chunks (as for the f16 kernel).
-static int launch_gemv_q8_auto(const void* x, const void* W, const float* w_scale, void* y, int N, int K, const GemvFusion& fu, cudaStream_t st) {
-    if ((K % 64) != 0) return NMT_ERR_UNSUPPORTED;
-    const int kc = K / 64;
-    int q = 1;
-    while (q < 64 && (kc + q - 1) / q > tune("gemv.unit_chunks", 7)) q *= 2;                                 // slices per row
-    if ((kc + q - 1) / q > kMmaMaxChunks) return NMT_ERR_UNSUPPORTED;
-    const int forced = tune("gemv.streams", 0);
-    int split = q >= 8 ? 8 : q, streams = q / split;
-    if (forced > 0 && forced <= 8 && q % forced == 0 && q / forced <= 8) { streams = forced; split = q / forced; }
-#define NMT_Q8_CASE(SP, ST) if (split == SP && streams == ST) return launch_gemv_q8<SP, ST>(x, W, w_scale, y, N, K, fu, st)
-    NMT_Q8_CASE(1, 1); NMT_Q8_CASE(2, 1); NMT_Q8_CASE(4, 1); NMT_Q8_CASE(8, 1);
-    NMT_Q8_CASE(1, 2); NMT_Q8_CASE(2, 2); NMT_Q8_CASE(4, 2); NMT_Q8_CASE(8, 2);
-    NMT_Q8_CASE(1, 4); NMT_Q8_CASE(2, 4); NMT_Q8_CASE(4, 4); NMT_Q8_CASE(8, 4);
-    NMT_Q8_CASE(1, 8); NMT_Q8_CASE(2, 8); NMT_Q8_CASE(4, 8); NMT_Q8_CASE(8, 8);
-#undef NMT_Q8_CASE
     return NMT_ERR_UNSUPPORTED;
 }
 
@@ -789,11 +568,6 @@ int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, con
     fu.residual = static_cast<const uint16_t*>(residual_bf16);
     // The prologue keeps a thread's share of x in 8 registers-vectors; the fused forms exist only on the tensor-core kernel.
     if (norm_w && (fu.norm_threads > kGemvWarps * 32 || (K / 8 + fu.norm_threads - 1) / fu.norm_threads > 8)) return NMT_ERR_UNSUPPORTED;
-    if (tune("gemv.variant", kDefaultGemvVariant) == 4) {
-        const int r = launch_gemv_q8_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
-                                          static_cast<cudaStream_t>(stream));
-        if (r != NMT_ERR_UNSUPPORTED) return r;
-    }
     return launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
                                 static_cast<cudaStream_t>(stream));
 }
@@ -809,10 +583,6 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
     const int kv = static_cast<int>(K / 16);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int variant = tune("gemv.variant", kDefaultGemvVariant);
-    if (variant == 4) {
-        const int r = launch_gemv_q8_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), GemvFusion{}, st);
-        if (r != NMT_ERR_UNSUPPORTED) return r;
-    }
     if (variant >= 3) {
         const int r = launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), GemvFusion{}, st);
         if (r != NMT_ERR_UNSUPPORTED) return r;

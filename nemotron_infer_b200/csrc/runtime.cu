@@ -38,7 +38,7 @@ static Knob g_knobs[] = {
     {"conv.pairs", {0}},          // causal conv1d: channel pairs per thread (2 = 8-byte vectors, 4 = 16-byte vectors)
     {"conv.unroll", {0}},         // causal conv1d: loads issued ahead of use (4 or 8)
     {"gemv.split", {0}},          // W8A16 GEMV: K-slices per row (1, 2, 4, 8); 0 = by K
-    {"gemv.variant", {0}},        // W8A16 GEMV: 4 = e4m3 MMA on the raw weight bytes, x as two e4m3 terms (default), 3 = f16 MMA, 1 = whole-unit CUDA-core loads, 2 = looped loads
+    {"gemv.variant", {0}},        // W8A16 GEMV: 3 = mma.sync inner product (default), 1 = whole-unit CUDA-core loads, 2 = looped loads
     {"gemv.early_trigger", {0}},  // W8A16 GEMV (mma): 1 (default) = let the next kernel launch once this one's last loads are issued, 2 = at the very end
     {"gemv.unit_chunks", {0}},    // W8A16 GEMV (mma): largest number of 64-k chunks per work unit (default 7)
     {"gemv.streams", {0}},        // W8A16 GEMV (mma): k-streams per 16-row tile (1, 2, 4, 8); 0 = by shape

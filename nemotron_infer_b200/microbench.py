@@ -3,6 +3,7 @@ in-test perf fixtures, tests/ops/test_reduce.cu:362-463, test_elementwise.cu:534
 
     python -m nemotron_infer_b200.microbench [--op all|add_rmsnorm|rmsnorm|gated|gated_model|relu2|add|embedding|chain]
                                              [--tokens T] [--reps R] [--warmup W] [--tune key=value ...]
+                                             [--graph] [--fixed-cost]
 
 Each op runs on buffer sets that are rotated so that consecutive launches never touch the same bytes and
 the sets together exceed twice the 126 MB L2.  Timing is by CUDA events on the launching stream around
@@ -163,6 +164,23 @@ def run_op(op: str, T: int, reps: int, warmup: int, dev, batch: int = 10, graph:
             "frac_of_measured_peak": round(gbs / peak, 4) if peak else None}
 
 
+def run_fixed_cost(op: str, T: int, reps: int, dev) -> dict:
+    """Separates a launch's steady cost from what does not grow with the number of launches: CUDA graphs of
+    n = 1 ... 32 back-to-back launches (rotating buffer sets), median replay time, least-squares line
+    time(n) = fixed + n * per_launch."""
+    pts = {}
+    for n in (1, 2, 4, 8, 16, 32):
+        r = run_op(op, T, reps, 3, dev, n, True)
+        pts[n] = r["median_us"] * n
+    xs, ys = list(pts), [pts[n] for n in pts]
+    mx, my = sum(xs) / len(xs), sum(ys) / len(ys)
+    slope = sum((a - mx) * (b - my) for a, b in zip(xs, ys)) / sum((a - mx) ** 2 for a in xs)
+    nbytes = SHAPES[op][1] * T
+    return {"op": op, "tokens": T, "us_by_launches": {str(k): round(v, 1) for k, v in pts.items()},
+            "per_launch_us": round(slope, 2), "fixed_us": round(my - slope * mx, 2),
+            "steady_gbs": round(nbytes / slope / 1e3, 1), "steady_frac_of_nominal_8000": round(nbytes / slope / 1e3 / NOMINAL_GBS, 4)}
+
+
 def run_chain(T: int, reps: int, dev) -> dict:
     """Latency of the whole 81-launch pass at a (small) token count: host-launched vs one CUDA-graph replay."""
     from . import chain
@@ -194,6 +212,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--batch", type=int, default=10, help="back-to-back launches per timed interval")
     ap.add_argument("--graph", action="store_true", help="capture each batch in a CUDA graph (default for the gemv ops)")
+    ap.add_argument("--fixed-cost", action="store_true", help="graphs of 1 ... 32 launches: per-launch cost and fixed cost of each op")
     ap.add_argument("--device", type=int, default=0)
     ap.add_argument("--tune", action="append", default=[], metavar="key=value")
     a = ap.parse_args()
@@ -208,6 +227,10 @@ def main() -> None:
             print(json.dumps(run_chain(a.tokens or 64, a.reps, f"cuda:{a.device}")), flush=True)
             continue
         T = a.tokens or SHAPES[op][0]
+        if a.fixed_cost:
+            print(json.dumps(run_fixed_cost(op, T, a.reps, f"cuda:{a.device}")), flush=True)
+            torch.cuda.empty_cache()
+            continue
         print(json.dumps(run_op(op, T, a.reps, a.warmup, f"cuda:{a.device}", a.batch, a.graph or op.startswith("gemv"))), flush=True)
         torch.cuda.empty_cache()
 
