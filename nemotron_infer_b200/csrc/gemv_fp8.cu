@@ -20,7 +20,7 @@
 namespace nmt {
 
 constexpr int kGemvWarps = 8;
-constexpr int kDefaultGemvVariant = 3;    // 3 = tensor-core inner product, 1 / 2 = CUDA-core kernels
+constexpr int kDefaultGemvVariant = 3;    // 5 = tcgen05 + TMA (gemv_umma.cu), 3 = mma.sync inner product, 1 / 2 = CUDA-core kernels
 
 // 4 e4m3 bytes (one 32-bit word) -> 4 floats, as two (lo, hi) pairs.
 __device__ __forceinline__ void e4m3x4_to_f32(uint32_t wd, float2& a, float2& b) {
@@ -521,6 +521,9 @@ static int launch_gemv_mma_auto(const void* x, const void* W, const float* w_sca
     return NMT_ERR_UNSUPPORTED;
 }
 
+int launch_gemv_umma(const void* x, const float* norm_w, float eps, const void* W, const float* w_scale, int activation,
+                     const void* residual, void* y, int N, int K, cudaStream_t st);      // gemv_umma.cu
+
 template <int SPLIT>
 static int launch_gemv(const void* x, const void* W, const float* w_scale, void* y, int N, int kv, cudaStream_t st) {
     constexpr int UNROLL = 4;
@@ -568,6 +571,11 @@ int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, con
     fu.residual = static_cast<const uint16_t*>(residual_bf16);
     // The prologue keeps a thread's share of x in 8 registers-vectors; the fused forms exist only on the tensor-core kernel.
     if (norm_w && (fu.norm_threads > kGemvWarps * 32 || (K / 8 + fu.norm_threads - 1) / fu.norm_threads > 8)) return NMT_ERR_UNSUPPORTED;
+    if (tune("gemv.variant", kDefaultGemvVariant) == 5) {
+        const int r = launch_gemv_umma(x_bf16, norm_w, eps, W_e4m3, w_scale, activation, residual_bf16, y_bf16, static_cast<int>(N),
+                                       static_cast<int>(K), static_cast<cudaStream_t>(stream));
+        if (r != NMT_ERR_UNSUPPORTED) return r;
+    }
     return launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
                                 static_cast<cudaStream_t>(stream));
 }
@@ -583,6 +591,10 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
     const int kv = static_cast<int>(K / 16);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int variant = tune("gemv.variant", kDefaultGemvVariant);
+    if (variant == 5) {
+        const int r = launch_gemv_umma(x_bf16, nullptr, 0.f, W_e4m3, w_scale, 0, nullptr, y_bf16, static_cast<int>(N), static_cast<int>(K), st);
+        if (r != NMT_ERR_UNSUPPORTED) return r;
+    }
     if (variant >= 3) {
         const int r = launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), GemvFusion{}, st);
         if (r != NMT_ERR_UNSUPPORTED) return r;

@@ -38,7 +38,9 @@ static Knob g_knobs[] = {
     {"conv.pairs", {0}},          // causal conv1d: channel pairs per thread (2 = 8-byte vectors, 4 = 16-byte vectors)
     {"conv.unroll", {0}},         // causal conv1d: loads issued ahead of use (4 or 8)
     {"gemv.split", {0}},          // W8A16 GEMV: K-slices per row (1, 2, 4, 8); 0 = by K
-    {"gemv.variant", {0}},        // W8A16 GEMV: 3 = mma.sync inner product (default), 1 = whole-unit CUDA-core loads, 2 = looped loads
+    {"gemv.variant", {0}},        // W8A16 GEMV: 5 = tcgen05.mma fed by TMA (x as two e4m3 terms), 3 = mma.sync inner product, 1 = whole-unit CUDA-core loads, 2 = looped loads
+    {"gemv.ring_stages", {0}},    // W8A16 GEMV (variant 5): 16 KB stages of the weight ring per CTA (default 4)
+    {"gemv.kparts", {0}},         // W8A16 GEMV (variant 5): CTAs per row tile that split K = cluster size, 1 / 2 / 4 / 8; 0 = by shape
     {"gemv.early_trigger", {0}},  // W8A16 GEMV (mma): 1 (default) = let the next kernel launch once this one's last loads are issued, 2 = at the very end
     {"gemv.unit_chunks", {0}},    // W8A16 GEMV (mma): largest number of 64-k chunks per work unit (default 7)
     {"gemv.streams", {0}},        // W8A16 GEMV (mma): k-streams per 16-row tile (1, 2, 4, 8); 0 = by shape

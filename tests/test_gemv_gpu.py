@@ -110,15 +110,43 @@ def test_tensor_core_path_keeps_small_elements_of_x_exact(ops):
         ops.tune("gemv.variant", 0)
 
 
+def test_tcgen05_path_splits_x_exactly_within_twelve_binades_of_its_maximum(ops):
+    """Variant 5 multiplies the e4m3 weights with x split into two e4m3 terms after scaling max|x| into [128, 256): every
+    element within 2^-12 of the largest must come back exactly (all 8 significant bits of the bf16), smaller ones with an
+    absolute error of at most 2^-17 of the largest."""
+    K = 64 * 18
+    mant = 1 + (torch.arange(K) % 128).float() / 128
+    expo = -(torch.arange(K) // 64).float()
+    x = (mant * torch.pow(torch.tensor(2.0), expo)).to(BF)
+    x[0] = 1.9921875
+    W = torch.zeros(K, K)
+    W[torch.arange(K), torch.arange(K)] = 1.0
+    Wq, sc = W.to(torch.float8_e4m3fn), torch.ones(K)
+    want = x.float()
+    try:
+        ops.tune("gemv.variant", 5)
+        got = ops.gemv_w8a16(x.cuda(), Wq.cuda(), sc.cuda()).float().cpu()
+    finally:
+        ops.tune("gemv.variant", 0)
+    exact = expo >= -12
+    assert torch.equal(got[exact], want[exact])
+    assert float((got - want).abs().max()) <= 2.0 ** -17 * 1.9921875
+
+
+@pytest.mark.parametrize("variant", [3, 5])
 @pytest.mark.parametrize("scale", [1e30, 1e-30, 3e4, 2.0 ** -20])
-def test_tensor_core_path_x_magnitudes(ops, scale):
+def test_tensor_core_path_x_magnitudes(ops, scale, variant):
     """x is staged as f16 times a power of two taken from max|x|: huge and tiny vectors must come out as accurately
     as ordinary ones."""
     g = torch.Generator().manual_seed(17)
     N, K = 96, 3136
     x = (torch.randn(K, generator=g) * scale).to(BF)
     W, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
-    got = ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()).float().cpu()
+    try:
+        ops.tune("gemv.variant", variant)
+        got = ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()).float().cpu()
+    finally:
+        ops.tune("gemv.variant", 0)
     want = og.gemv_w8a16(x, W, sc).float()
     rep = og.ulp_report(got.to(BF), want.to(BF))
     assert rep["mismatch_frac"] <= 0.05 and rep["max_ulp"] <= 4, rep
@@ -126,7 +154,7 @@ def test_tensor_core_path_x_magnitudes(ops, scale):
 
 @pytest.mark.parametrize("N,K", [(40, 64), (9, 192), (300, 16384), (50, 16448), (1000, 512), (17, 32704), (5000, 3136),
                                  (1237, 12544), (333, 7680), (148 * 8 + 1, 128)])
-def test_tensor_core_path_slicing(ops, N, K):
+def test_tensor_core_path_slicing(ops, built_lib, N, K):
     """Shapes that exercise one chunk per row, uneven slices, the register-held and re-read x staging, many
     k-streams per tile and ragged last tiles; every stream count the knob allows."""
     g = torch.Generator().manual_seed(N * 7 + K)
@@ -141,15 +169,33 @@ def test_tensor_core_path_slicing(ops, N, K):
                     ops.tune("gemv.unit_chunks", chunks)
                     ops.tune("gemv.ctas_per_sm", per_sm)
                     check(ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()), want)
-    finally:
         for k in ("gemv.streams", "gemv.unit_chunks", "gemv.ctas_per_sm"):
             ops.tune(k, 0)
+        ops.tune("gemv.variant", 5)                  # tcgen05 + TMA; shapes it does not take fall through to the default
+        for kparts in (0, 1, 2, 4, 8):
+            for stages in (0, 1, 2, 7):
+                ops.tune("gemv.kparts", kparts)
+                ops.tune("gemv.ring_stages", stages)
+                check(ops.gemv_w8a16(x.cuda(), W.cuda(), sc.cuda()), want)
+    finally:
+        for k in ("gemv.streams", "gemv.unit_chunks", "gemv.ctas_per_sm", "gemv.variant", "gemv.kparts", "gemv.ring_stages"):
+            ops.tune(k, 0)
+    assert built_lib.nmt_device_wait_timeouts() == 0
 
 
+@pytest.mark.parametrize("variant", [3, 5])
 @pytest.mark.parametrize("N,K", [(12544, 3136), (3136, 12544), (17504, 3136), (3136, 7680), (40, 64), (16, 10240)])
-def test_fused_decode_forms_are_byte_identical_to_the_separate_ops(ops, N, K):
+def test_fused_decode_forms_are_byte_identical_to_the_separate_ops(ops, N, K, variant):
     """norm -> GEMV -> relu^2 / residual add as one launch: same bytes as this library's separate kernels, and the
-    oracle's composition of the same steps within the GEMV tolerance."""
+    oracle's composition of the same steps within the GEMV tolerance.  Both tensor-core kernels."""
+    ops.tune("gemv.variant", variant)
+    try:
+        _fused_forms(ops, N, K, variant)
+    finally:
+        ops.tune("gemv.variant", 0)
+
+
+def _fused_forms(ops, N, K, variant):
     g = torch.Generator().manual_seed(N + 3 * K)
     x = (2 * torch.randn(K, generator=g)).to(BF)
     nw = og.norm_weight(K, g)
@@ -165,7 +211,8 @@ def test_fused_decode_forms_are_byte_identical_to_the_separate_ops(ops, N, K):
         "relu2": (dict(activation="relu2"), ops.relu2(ops.gemv_w8a16(xd, Wd, scd))),
         "norm+relu2+residual": (dict(norm_w=nwd, activation="relu2", residual=resd), ops.add(resd, ops.relu2(y_plain))),
     }
-    with_norm = K <= 10240                               # the norm prologue exists up to 10,240 columns (the model norms 3136)
+    # the norm prologue exists up to 10,240 columns (the model norms 3136); the tcgen05 kernel runs it on four warps: 5,120
+    with_norm = K <= (10240 if variant == 3 else 5120)
     for name, (kw, want) in cases.items():
         if "norm" in name and not with_norm:
             continue
