@@ -22,6 +22,10 @@
 //   mamba_block_decode_fp8     (model/mamba_block.cuh:439-516) norm + the three in_proj slices in one launch
 //                              (:473-481), conv step + split (:484-496), out_proj + residual add (:508-514) -
 //                              5 launches for 12
+//   attention_block_forward_fp8 (model/attention_block.cuh:286-358) norm -> quantise in one entry point (:328-330)
+//   attention_block_decode_fp8  (model/attention_block.cuh:363-414) the pre-norm inside each of the q / k / v GEMVs
+//                              (:396-401), o_proj + residual add in one launch (:408-413) - 4 launches of this
+//                              library for 6
 // Every fused form returns what the reference's sequence of this library's single ops returns, byte for byte
 // (the entry points are tested for exactly that), so swapping a block changes its traffic, not its numbers.
 #ifndef NEMOTRON_B200_SHIM_BLOCKS_CUH
@@ -55,6 +59,8 @@ inline void quantize_activation_fp8(const __nv_bfloat16* x_bf16, __nv_fp8_e4m3* 
 #define mamba_block_decode_bf16 mamba_block_decode_bf16_reference
 #define mamba_block_forward_fp8 mamba_block_forward_fp8_reference
 #define mamba_block_decode_fp8 mamba_block_decode_fp8_reference
+#define attention_block_forward_fp8 attention_block_forward_fp8_reference
+#define attention_block_decode_fp8 attention_block_decode_fp8_reference
 #include "tensor/tensor.h"
 #include "tensor/allocator.cuh"
 #include "model/mlp_block.cuh"
@@ -65,6 +71,8 @@ inline void quantize_activation_fp8(const __nv_bfloat16* x_bf16, __nv_fp8_e4m3* 
 #undef mamba_block_decode_bf16
 #undef mamba_block_forward_fp8
 #undef mamba_block_decode_fp8
+#undef attention_block_forward_fp8
+#undef attention_block_decode_fp8
 
 namespace nemotron::model {
 
@@ -265,6 +273,80 @@ inline void mamba_block_decode_fp8(const __nv_bfloat16* input, const Mamba2Block
         ops::rmsnorm_gated_bf16<G>(y, gnormed, w.gnorm_w, gate, 1, INTER, INTER / G, EPS, stream);
         ok(nmt_gemv_w8a16_fused(gnormed, nullptr, 0.f, w.out_proj_w, w.out_proj_wscale, 0, input, out, HIDDEN, INTER, stream),
            "nmt_gemv_w8a16_fused(out_proj, residual)");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Attention, FP8 weights.  Only the steps around the projections change; the transposes, the SDPA kernels and the KV
+// cache writes are the reference's (model/attention_block.cuh:44-95, ops/attention/*).
+// ---------------------------------------------------------------------------------------------------------------
+template <int HIDDEN, int H_Q, int H_KV, int HEAD = 128>
+inline void attention_block_forward_fp8(const __nv_bfloat16* input, const AttnBlockWeightsFP8& w, __nv_bfloat16* out, int S,
+                                        __nv_bfloat16* k_cache = nullptr, __nv_bfloat16* v_cache = nullptr, int cache_cap = 0,
+                                        cudaStream_t stream = nullptr) {
+    using namespace b200;
+    namespace att = nemotron::ops::attention;
+    constexpr int QD = H_Q * HEAD, KD = H_KV * HEAD;
+    constexpr float EPS = 1e-5f;
+    if (S <= 0) return;
+    if (cache_cap <= 0) cache_cap = S;
+    const size_t rows = static_cast<size_t>(S);
+    fp8* norm_q = scratch<fp8>(rows * HIDDEN);
+    bf16* q = scratch<bf16>(rows * QD);
+    bf16* k = scratch<bf16>(rows * KD);
+    bf16* v = scratch<bf16>(rows * KD);
+    bf16* qt = scratch<bf16>(rows * QD);
+    bf16* kt = scratch<bf16>(rows * KD);
+    bf16* vt = scratch<bf16>(rows * KD);
+    bf16* ot = scratch<bf16>(rows * QD);
+    bf16* o = scratch<bf16>(rows * QD);
+    fp8* o_q = scratch<fp8>(rows * QD);
+    bf16* attn = scratch<bf16>(rows * HIDDEN);
+    float* scales = scratch<float>(2);
+    unsigned int* amax = scratch<unsigned int>(1);
+    char* stats = scratch<char>(nmt_fp8_workspace_bytes(S));
+    char* lt = scratch<char>(static_cast<int64_t>(kLtWorkspace));
+    ok(nmt_rmsnorm_quant_fp8(input, w.block_norm_w, norm_q, scales, stats, S, HIDDEN, EPS, stream), "nmt_rmsnorm_quant_fp8");
+    ops::gemm_fp8(norm_q, w.q_proj_w, q, scales, w.q_proj_wscale, S, QD, HIDDEN, lt, kLtWorkspace, stream);
+    ops::gemm_fp8(norm_q, w.k_proj_w, k, scales, w.k_proj_wscale, S, KD, HIDDEN, lt, kLtWorkspace, stream);
+    ops::gemm_fp8(norm_q, w.v_proj_w, v, scales, w.v_proj_wscale, S, KD, HIDDEN, lt, kLtWorkspace, stream);
+    attn_transpose_shd_to_hsd_launch<bf16>(q, qt, S, H_Q, HEAD, stream);
+    attn_transpose_shd_to_hsd_launch<bf16>(k, kt, S, H_KV, HEAD, stream);
+    attn_transpose_shd_to_hsd_launch<bf16>(v, vt, S, H_KV, HEAD, stream);
+    att::sdpa_prefill_bf16<32, HEAD>(qt, kt, vt, ot, S, H_Q, H_KV, stream);
+    attn_transpose_hsd_to_shd_launch<bf16>(ot, o, S, H_Q, HEAD, stream);
+    ops::quantize_activation_fp8(o, o_q, scales + 1, amax, rows * QD, stream);       // this library's quantiser (replaced above)
+    ops::gemm_fp8(o_q, w.o_proj_w, attn, scales + 1, w.o_proj_wscale, S, HIDDEN, QD, lt, kLtWorkspace, stream);
+    ops::elementwise_ops_bf16<ops::kElementwiseAdd>(input, attn, out, rows * HIDDEN, 1.f, nullptr, 0.f, 1.f, stream);
+    if (k_cache && v_cache) {                                      // [H_KV, cache_cap, HEAD] caches take the first S positions
+        const size_t row_bytes = static_cast<size_t>(S) * HEAD * sizeof(bf16), pitch = static_cast<size_t>(cache_cap) * HEAD * sizeof(bf16);
+        cudaMemcpy2DAsync(k_cache, pitch, kt, row_bytes, row_bytes, H_KV, cudaMemcpyDeviceToDevice, stream);
+        cudaMemcpy2DAsync(v_cache, pitch, vt, row_bytes, row_bytes, H_KV, cudaMemcpyDeviceToDevice, stream);
+    }
+}
+
+template <int HIDDEN, int H_Q, int H_KV, int HEAD = 128>
+inline void attention_block_decode_fp8(const __nv_bfloat16* input, const AttnBlockWeightsFP8& w, __nv_bfloat16* k_cache,
+                                       __nv_bfloat16* v_cache, int S_cache, int cache_cap, __nv_bfloat16* out,
+                                       cudaStream_t stream = nullptr) {
+    using namespace b200;
+    namespace att = nemotron::ops::attention;
+    constexpr int QD = H_Q * HEAD, KD = H_KV * HEAD;
+    constexpr float EPS = 1e-5f;
+    if constexpr (HIDDEN % 64 != 0 || QD % 64 != 0 || HIDDEN > 10240) {
+        return attention_block_decode_fp8_reference<HIDDEN, H_Q, H_KV, HEAD>(input, w, k_cache, v_cache, S_cache, cache_cap, out, stream);
+    } else {
+        bf16* q = scratch<bf16>(QD);
+        bf16* knew = scratch<bf16>(KD);
+        bf16* vnew = scratch<bf16>(KD);
+        bf16* ot = scratch<bf16>(QD);
+        // q, k and v are three matrices, so three GEMVs; each normalises its own copy of the token (a 3136-wide row), which
+        // is cheaper than a launch of its own for the norm
+        ok(nmt_gemv_w8a16_fused(input, w.block_norm_w, EPS, w.q_proj_w, w.q_proj_wscale, 0, nullptr, q, QD, HIDDEN, stream), "nmt_gemv_w8a16_fused(norm, q_proj)");
+        ok(nmt_gemv_w8a16_fused(input, w.block_norm_w, EPS, w.k_proj_w, w.k_proj_wscale, 0, nullptr, knew, KD, HIDDEN, stream), "nmt_gemv_w8a16_fused(norm, k_proj)");
+        ok(nmt_gemv_w8a16_fused(input, w.block_norm_w, EPS, w.v_proj_w, w.v_proj_wscale, 0, nullptr, vnew, KD, HIDDEN, stream), "nmt_gemv_w8a16_fused(norm, v_proj)");
+        att::sdpa_decode_bf16<HEAD>(q, k_cache, v_cache, ot, knew, vnew, S_cache, cache_cap, H_Q, H_KV, stream);
+        ok(nmt_gemv_w8a16_fused(ot, nullptr, 0.f, w.o_proj_w, w.o_proj_wscale, 0, input, out, HIDDEN, QD, stream), "nmt_gemv_w8a16_fused(o_proj, residual)");
     }
 }
 

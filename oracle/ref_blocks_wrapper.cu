@@ -136,6 +136,26 @@ BLK_API int blk_attn_decode_bf16(const void* in, const float* norm_w, const void
     return last_error();
 }
 
+BLK_API int blk_attn_forward_fp8(const void* in, const float* norm_w, const void* q_w, const float* q_s, const void* k_w,
+                                 const float* k_s, const void* v_w, const float* v_s, const void* o_w, const float* o_s, void* out,
+                                 int S, void* k_cache, void* v_cache, int cache_cap) {
+    AttnBlockWeightsFP8 w{norm_w, static_cast<const fp8*>(q_w), q_s, static_cast<const fp8*>(k_w), k_s, static_cast<const fp8*>(v_w), v_s,
+                          static_cast<const fp8*>(o_w), o_s};
+    attention_block_forward_fp8<ATTN_CFG>(static_cast<const bf16*>(in), w, static_cast<bf16*>(out), S, static_cast<bf16*>(k_cache),
+                                          static_cast<bf16*>(v_cache), cache_cap, nullptr);
+    return last_error();
+}
+
+BLK_API int blk_attn_decode_fp8(const void* in, const float* norm_w, const void* q_w, const float* q_s, const void* k_w,
+                                const float* k_s, const void* v_w, const float* v_s, const void* o_w, const float* o_s,
+                                void* k_cache, void* v_cache, int S_cache, int cache_cap, void* out) {
+    AttnBlockWeightsFP8 w{norm_w, static_cast<const fp8*>(q_w), q_s, static_cast<const fp8*>(k_w), k_s, static_cast<const fp8*>(v_w), v_s,
+                          static_cast<const fp8*>(o_w), o_s};
+    attention_block_decode_fp8<ATTN_CFG>(static_cast<const bf16*>(in), w, static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), S_cache,
+                                         cache_cap, static_cast<bf16*>(out), nullptr);
+    return last_error();
+}
+
 // The activation quantiser the blocks call (ops/gemm.cuh:291-307; this library's in the fused build).
 BLK_API int blk_quantize_activation_fp8(const void* x, void* out, float* scale, unsigned int* amax, size_t n) {
     nemotron::ops::quantize_activation_fp8(static_cast<const bf16*>(x), static_cast<fp8*>(out), scale, amax, n, nullptr);

@@ -299,3 +299,56 @@ def test_mamba_fp8_decode_fused_equals_unfused_bit_for_bit(built_lib):
     assert (res["shim"][0].float() - res["fused"][0].float()).abs().max().item() < 5e-2
     assert torch.equal(res["shim"][1], res["fused"][1]), "conv window"
     assert rel_l2(res["fused"][2], res["shim"][2]) < 2e-2
+
+
+def _attn_fp8_weights(g):
+    out = []
+    for k in ("q", "k", "v", "o"):
+        out.extend(p(t) for t in _keep(fp8_rows(g[k])))
+    return out
+
+
+_KEPT = []
+
+
+def _keep(ts):
+    _KEPT.append(ts)          # the pointers handed to the block must outlive the launches
+    return ts
+
+
+@pytest.mark.parametrize("which", ["stock", "shim", "fused"])
+def test_attention_fp8_prefill_then_decode(built_lib, which):
+    """model/attention_block.cuh:286-414 at the tolerances of tests/model/test_attention_block.cu:161-300: the full
+    sequence, then prefill of S-1 tokens into the KV cache and a decode step for token S."""
+    lib, g = load_blocks(which), attn_fixture()
+    S = 40
+    x = g["x"].to(BF)
+    w = _attn_fp8_weights(g)
+    before = built_lib.nmt_launch_count()
+    full = torch.empty(S, 256, dtype=BF, device="cuda")
+    assert lib.blk_attn_forward_fp8(p(x), p(g["nw"]), *w, p(full), S, None, None, 0) == 0
+    lib.blk_reset_allocator()
+    kc = torch.zeros(2, S, 128, dtype=BF, device="cuda")
+    vc = torch.zeros(2, S, 128, dtype=BF, device="cuda")
+    pre = torch.empty(S - 1, 256, dtype=BF, device="cuda")
+    assert lib.blk_attn_forward_fp8(p(x), p(g["nw"]), *w, p(pre), S - 1, p(kc), p(vc), S) == 0
+    lib.blk_reset_allocator()
+    tok = x[S - 1].contiguous()
+    dec = torch.empty(256, dtype=BF, device="cuda")
+    assert lib.blk_attn_decode_fp8(p(tok), p(g["nw"]), *w, p(kc), p(vc), S - 1, S, p(dec)) == 0
+    torch.cuda.synchronize()
+    lib.blk_free_allocator()
+    launched = built_lib.nmt_launch_count() - before
+    assert rel_l2(full, g["want"]) < 0.3
+    assert rel_l2(pre, g["want"][:S - 1]) < 0.3
+    assert rel_l2(dec, g["want"][S - 1]) < 0.35
+    # shim (the reference's own quantiser): per prefill norm and add = 2; decode norm, 4 GEMVs, add = 6
+    # fused: per prefill norm+quantise (2), quantiser (2), add = 5; decode 3 GEMVs with the norm inside, o_proj GEMV + add = 4
+    assert launched == {"stock": 0, "shim": 10, "fused": 14}[which]
+    return full, pre, dec
+
+
+def test_attention_fp8_fused_equals_unfused_bit_for_bit(built_lib):
+    res = {which: test_attention_fp8_prefill_then_decode(built_lib, which) for which in ("shim", "fused")}
+    for a, b, name in zip(res["shim"], res["fused"], ("full sequence", "prefill", "decode")):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), name
