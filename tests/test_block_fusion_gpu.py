@@ -316,8 +316,7 @@ def _keep(ts):
     return ts
 
 
-@pytest.mark.parametrize("which", ["stock", "shim", "fused"])
-def test_attention_fp8_prefill_then_decode(built_lib, which):
+def _attention_fp8_prefill_then_decode(built_lib, which):
     """model/attention_block.cuh:286-414 at the tolerances of tests/model/test_attention_block.cu:161-300: the full
     sequence, then prefill of S-1 tokens into the KV cache and a decode step for token S."""
     lib, g = load_blocks(which), attn_fixture()
@@ -348,7 +347,12 @@ def test_attention_fp8_prefill_then_decode(built_lib, which):
     return full, pre, dec
 
 
+@pytest.mark.parametrize("which", ["stock", "shim", "fused"])
+def test_attention_fp8_prefill_then_decode(built_lib, which):
+    _attention_fp8_prefill_then_decode(built_lib, which)
+
+
 def test_attention_fp8_fused_equals_unfused_bit_for_bit(built_lib):
-    res = {which: test_attention_fp8_prefill_then_decode(built_lib, which) for which in ("shim", "fused")}
+    res = {which: _attention_fp8_prefill_then_decode(built_lib, which) for which in ("shim", "fused")}
     for a, b, name in zip(res["shim"], res["fused"], ("full sequence", "prefill", "decode")):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16)), name
