@@ -101,7 +101,8 @@ int nmt_add_rmsnorm_bf16(const void* x, const void* r, const float* w,
  *                                     announces the norm weight of block i+1.  NULL withdraws the announcement.
  *   nmt_block_head_rmsnorm_bf16       what the drop-in rmsnorm_bf16 calls: nmt_rmsnorm_bf16, except that it launches
  *                                     NOTHING when the previous block's fused tail already wrote exactly this tensor
- *                                     (same x, y, w, shape, eps and stream).
+ *                                     (same x, y, w, shape, eps and stream) AND no other entry point of this library
+ *                                     has launched a kernel from this thread since that tail.
  *   nmt_block_tail_add_bf16           what the drop-in residual add calls: nmt_add_bf16, except that with a weight
  *                                     announced it launches nmt_add_rmsnorm_bf16 instead and writes rmsnorm(out) *
  *                                     w_next over THIS block's pre-norm tensor (the y of its head call).

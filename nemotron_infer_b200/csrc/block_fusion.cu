@@ -20,7 +20,9 @@
 //
 // Anything that does not match (a different address after the allocator grew a slab, another stream, no
 // announcement) simply runs the plain kernels: the result is the same either way, only the traffic differs.  The
-// record of a fused tail is dropped by the next head call whatever its outcome, and by nmt_fusion_reset().
+// record of a fused tail is dropped by the next head call whatever its outcome, by nmt_fusion_reset(), and by ANY
+// other entry point of this library that launches a kernel from this thread in between (it might have written the
+// rows or the normed tensor): a head is skipped only when it is the very next launch after the fused tail.
 // State is per host thread (the reference drives its layers from one thread, binding.cu holds the GIL).
 #include "nmt_common.cuh"
 
@@ -33,6 +35,7 @@ struct NormRecord {
     int64_t rows = 0, cols = 0;
     float eps = 0.f;
     cudaStream_t st = nullptr;
+    int64_t epoch = 0;            // thread_launch_epoch() right after the launch that produced y
     bool valid = false;
 };
 struct FusionState {
@@ -80,7 +83,7 @@ int nmt_block_head_rmsnorm_bf16(const void* x, void* y, const float* w, int64_t 
     f.ready.valid = false;                       // one use only, whatever happens next
     f.head.valid = false;
     const bool done_already = r.valid && rows > 0 && r.x == x && r.y == y && r.w == w && r.rows == rows &&
-                              r.cols == cols && r.eps == eps && r.st == st;
+                              r.cols == cols && r.eps == eps && r.st == st && r.epoch == nmt::thread_launch_epoch();
     if (!done_already) {
         const int s = nmt_rmsnorm_bf16(x, y, w, rows, cols, eps, stream);
         if (s != NMT_OK) return s;
@@ -106,7 +109,7 @@ int nmt_block_tail_add_bf16(const void* a, const void* b, void* out, int64_t n, 
         const int s = nmt_add_rmsnorm_bf16(a, b, f.next_w, out, h.y, h.rows, h.cols, f.next_eps, stream);
         if (s == NMT_OK) {
             f.ready.x = out; f.ready.y = h.y; f.ready.w = f.next_w; f.ready.rows = h.rows; f.ready.cols = h.cols;
-            f.ready.eps = f.next_eps; f.ready.st = st; f.ready.valid = true;
+            f.ready.eps = f.next_eps; f.ready.st = st; f.ready.epoch = nmt::thread_launch_epoch(); f.ready.valid = true;
             ++f.fused_tails;
             return NMT_OK;
         }

@@ -143,6 +143,7 @@ inline bool aligned4(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 3
 
 extern std::atomic<int64_t> g_launches;
 int finish_launch(int n_kernels);   // records cudaGetLastError(); returns an nmt_status
+int64_t thread_launch_epoch();     // how many calls of this host thread have launched kernels so far
 int tune(const char* key, int dflt);  // current value of a tuning knob
 
 bool pdl_enabled();   // runtime.cu: knob "launch.pdl"

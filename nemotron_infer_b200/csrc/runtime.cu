@@ -8,6 +8,8 @@ namespace nmt {
 
 std::atomic<int64_t> g_launches{0};
 static thread_local char t_cuda_err[256] = "";
+static thread_local int64_t t_launch_epoch = 0;
+int64_t thread_launch_epoch() { return t_launch_epoch; }
 
 int finish_launch(int n_kernels) {
     cudaError_t e = cudaGetLastError();
@@ -16,6 +18,7 @@ int finish_launch(int n_kernels) {
         return NMT_ERR_LAUNCH;
     }
     g_launches.fetch_add(n_kernels, std::memory_order_relaxed);
+    if (n_kernels > 0) ++t_launch_epoch;
     return NMT_OK;
 }
 
@@ -81,7 +84,10 @@ int64_t read_wait_timeouts() {
     return total;
 }
 
-bool pdl_enabled() { return g_knobs[0].value.load(std::memory_order_relaxed) != 2; }
+bool pdl_enabled() {
+    static Knob* const k = find_knob("launch.pdl");
+    return k->value.load(std::memory_order_relaxed) != 2;
+}
 
 int tune(const char* key, int dflt) {
     Knob* k = find_knob(key);

@@ -154,6 +154,44 @@ def test_fusion_falls_back_when_the_pattern_does_not_match(built_lib):
     built_lib.nmt_fusion_reset()
 
 
+def test_a_launch_between_the_fused_tail_and_the_head_drops_the_pending_norm(built_lib):
+    """The head is skipped only when it is the very next launch of this library on the thread: here relu^2 rewrites the
+    rows in between, and the head must run its norm on the new rows."""
+    T, H = 64, 3136
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(T, H, generator=g, device="cuda").to(BF)
+    m = torch.randn(T, H, generator=g, device="cuda").to(BF)
+    w1 = (1 + 0.1 * torch.randn(H, generator=g, device="cuda")).contiguous()
+    w2 = (1 + 0.1 * torch.randn(H, generator=g, device="cuda")).contiguous()
+    y, out, want = (torch.empty(T, H, dtype=BF, device="cuda") for _ in range(3))
+    built_lib.nmt_fusion_reset()
+    f0, e0 = fusion_counters(built_lib)
+    assert built_lib.nmt_block_head_rmsnorm_bf16(p(x), p(y), p(w1), T, H, EPS, None) == 0
+    assert built_lib.nmt_fuse_next_norm(p(w2), EPS) == 0
+    assert built_lib.nmt_block_tail_add_bf16(p(x), p(m), p(out), T * H, None) == 0          # fused: y = norm(out) * w2
+    assert built_lib.nmt_relu2_bf16(p(out), p(out), T * H, None) == 0                       # rows change under it
+    assert built_lib.nmt_block_head_rmsnorm_bf16(p(out), p(y), p(w2), T, H, EPS, None) == 0
+    assert built_lib.nmt_rmsnorm_bf16(p(out), p(want), p(w2), T, H, EPS, None) == 0
+    torch.cuda.synchronize()
+    f1, e1 = fusion_counters(built_lib)
+    assert (f1 - f0, e1 - e0) == (1, 0)
+    assert torch.equal(y.view(torch.int16), want.view(torch.int16))
+    # and with nothing in between the same sequence does skip the head
+    assert built_lib.nmt_block_head_rmsnorm_bf16(p(x), p(y), p(w1), T, H, EPS, None) == 0
+    assert built_lib.nmt_fuse_next_norm(p(w2), EPS) == 0
+    assert built_lib.nmt_block_tail_add_bf16(p(x), p(m), p(out), T * H, None) == 0
+    assert built_lib.nmt_block_head_rmsnorm_bf16(p(out), p(y), p(w2), T, H, EPS, None) == 0
+    assert built_lib.nmt_rmsnorm_bf16(p(out), p(want), p(w2), T, H, EPS, None) == 0
+    torch.cuda.synchronize()
+    f2, e2 = fusion_counters(built_lib)
+    assert (f2 - f1, e2 - e1) == (1, 1)
+    # y now comes from the fused kernel, which spreads a row over another number of threads than the plain norm:
+    # the two may differ by one bf16 ulp in a few elements (summation order)
+    rep = og.ulp_report(y.cpu(), want.cpu())
+    assert rep["max_ulp"] <= 1 and rep["mismatch_frac"] <= 0.005, rep
+    built_lib.nmt_fusion_reset()
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # FP8 and single-token block forms
 # ---------------------------------------------------------------------------------------------------------------
