@@ -163,20 +163,27 @@ class ChainPass:
 
     def run(self) -> torch.Tensor:
         """Enqueues one pass on torch's current stream; returns the final normed hidden states [T, HIDDEN]."""
+        self._enqueue_rows(0, self.tokens)
+        return self.buf.normed
+
+    def _enqueue_rows(self, lo: int, hi: int) -> None:
+        """The 81 launches on rows [lo, hi) of every resident tensor (tokens are independent: a row range of the
+        pass is the pass of that row range)."""
         b = self.buf
-        cur, other = b.hidden
-        ops.embedding(b.table, b.ids, out=cur, err_flag=b.err_flag)
+        cur, other = b.hidden[0][lo:hi], b.hidden[1][lo:hi]
+        mixer = [m[lo:hi] for m in b.mixer_out]
+        y, z, gated_out, u, act, normed = b.y[lo:hi], b.z[lo:hi], b.gated_out[lo:hi], b.u[lo:hi], b.act[lo:hi], b.normed[lo:hi]
+        ops.embedding(b.table, b.ids[lo:hi], out=cur, err_flag=b.err_flag)
         n_m = 0
         for i, kind in enumerate(self.schedule):
             if kind == "M":
-                ops.rmsnorm_gated(b.y, b.z, b.gated_w[n_m], D_INNER // N_GROUPS, out=b.gated_out)
+                ops.rmsnorm_gated(y, z, b.gated_w[n_m], D_INNER // N_GROUPS, out=gated_out)
                 n_m += 1
             elif kind == "-":
-                ops.relu2(b.u, out=b.act)
-            ops.add_rmsnorm(cur, b.mixer_out[i % len(b.mixer_out)], b.norm_w[i], out_res=other, out=b.normed)
+                ops.relu2(u, out=act)
+            ops.add_rmsnorm(cur, mixer[i % len(mixer)], b.norm_w[i], out_res=other, out=normed)
             cur, other = other, cur
-        self.final_hidden = cur
-        return b.normed
+        self.final_hidden = b.hidden[len(self.schedule) % 2]      # the buffers swap once per layer
 
     def capture(self) -> None:
         """Records the 81-launch pass into a CUDA graph.  For decode-sized shards (T = 1 ... 64) the pass is
@@ -195,15 +202,53 @@ class ChainPass:
         self.graph.replay()
         return self.buf.normed
 
-    def run_from_host(self, ids_host: torch.Tensor, full_output: torch.Tensor | None = None) -> torch.Tensor:
+    def capture_pipelined(self, full_output: torch.Tensor, chunks: int) -> None:
+        """Records the pass as `chunks` row ranges, each followed by the copy of its normed rows to `full_output`
+        (pinned host memory) on a second stream, so that a range travels to the host while the next one is computed.
+        One graph; `full_output` must be the same tensor on every replay."""
+        T = self.tokens
+        bounds = [shard_range(T, c, chunks) for c in range(chunks)]
+        side = torch.cuda.Stream(device=self.device)
+        self.run()                                   # one-time kernel attributes, outside the capture
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            main = torch.cuda.current_stream()
+            for lo, hi in bounds:
+                if hi <= lo:
+                    continue
+                self._enqueue_rows(lo, hi)
+                done = torch.cuda.Event()
+                done.record(main)
+                side.wait_event(done)
+                with torch.cuda.stream(side):
+                    full_output[lo:hi].copy_(self.buf.normed[lo:hi], non_blocking=True)
+            joined = torch.cuda.Event()
+            joined.record(side)
+            main.wait_event(joined)
+        self._pipe = (graph, full_output.data_ptr(), chunks)
+
+    def run_from_host(self, ids_host: torch.Tensor, full_output: torch.Tensor | None = None, chunks: int | None = None) -> torch.Tensor:
         """The end-to-end call: token ids arrive in (pinned) host memory, the last token's normed hidden
         state comes back to host memory — what the engine's prefill hands to lm_head (engine.py:241-251).
         The pass is the captured graph when capture() has been called, host-launched otherwise.  With
-        `full_output` (a pinned [T, HIDDEN] bf16 host tensor) every normed row is copied back instead."""
+        `full_output` (a pinned [T, HIDDEN] bf16 host tensor) every normed row is copied back instead: in `chunks`
+        row ranges whose copies overlap the next range's kernels (default: 4 ranges from 32,768 tokens up, else 1)."""
         b = self.buf
         if self._host_out is None:
             self._host_out = torch.empty(HIDDEN, dtype=torch.bfloat16).pin_memory()
         b.ids.copy_(ids_host, non_blocking=True)
+        if full_output is not None:
+            if chunks is None:
+                chunks = 4 if self.tokens >= 32768 else 1
+            if chunks > 1 and full_output.is_pinned():
+                pipe = getattr(self, "_pipe", None)
+                if pipe is None or pipe[1] != full_output.data_ptr() or pipe[2] != chunks:
+                    self.capture_pipelined(full_output, chunks)
+                    b.ids.copy_(ids_host, non_blocking=True)
+                self._pipe[0].replay()
+                torch.cuda.current_stream().synchronize()
+                return full_output
         normed = self.replay() if getattr(self, "graph", None) is not None else self.run()
         if full_output is not None:
             full_output.copy_(normed, non_blocking=True)

@@ -123,6 +123,15 @@ def test_bench_parity_sample_and_batch_shards(built_lib):
     assert torch.equal(last.view(torch.int16), ref[G - 1].cpu().view(torch.int16))
     assert torch.equal(whole.run_from_host(ids_host, full_output=rows_host).view(torch.int16), ref.cpu().view(torch.int16))
     assert whole.graph_launches == 81
+    # ... also as three row ranges whose copies to the host overlap the next range's kernels (one graph, two streams)
+    rows_host.zero_()
+    launches = built_lib.nmt_launch_count()
+    got = whole.run_from_host(ids_host, full_output=rows_host, chunks=3)
+    assert built_lib.nmt_launch_count() - launches == 81 + 3 * 81          # one warm-up pass, then three ranges captured
+    assert torch.equal(got.view(torch.int16), ref.cpu().view(torch.int16))
+    rows_host.zero_()
+    assert torch.equal(whole.run_from_host(ids_host, full_output=rows_host, chunks=3).view(torch.int16), ref.cpu().view(torch.int16))
+    assert torch.equal(whole.final_hidden.view(torch.int16), whole.buf.hidden[0].view(torch.int16))
     # a wrong byte in the residual stream or the activation is reported
     whole.final_hidden[0, 0] += 1.0
     whole.buf.normed[G - 1, 5] = 1000.0
