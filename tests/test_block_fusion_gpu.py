@@ -245,6 +245,50 @@ def test_fp8_mlp_block_at_model_width_prefill_and_single_token(built_lib):
             assert launches == {"stock": 0, "shim": 3, "fused": 5}
 
 
+def test_single_token_fp8_mlp_block_latency_three_ways(built_lib):
+    """The reference's FP8 MLP block for one token at model width, timed on the device: on the reference's own kernels
+    (5 launches), on this library's single ops (5 launches) and in fused form (2 launches).  Four weight sets (4 x 79 MB)
+    rotate so that no call finds its matrices in L2, as in a 42-layer decode step.  The figures go to the session's
+    report; the assertions are only the order and a factor of two over the reference's kernels."""
+    from conftest import ULP_LOG
+    H, I, SETS, CALLS = 3136, 12544, 4, 48
+    g = torch.Generator().manual_seed(6)
+    nw = (1 + 0.1 * torch.randn(H, generator=g)).cuda()
+    x = torch.randn(1, H, generator=g).to(BF).cuda()
+    sets = []
+    for _ in range(SETS):
+        upq, ups = fp8_rows(0.02 * torch.randn(I, H, generator=g))
+        downq, downs = fp8_rows(0.02 * torch.randn(H, I, generator=g))
+        sets.append((upq, ups, downq, downs))
+    out = torch.empty_like(x)
+    us = {}
+    for which in ("stock", "shim", "fused"):
+        lib = load_blocks(which)
+
+        def call(i):
+            upq, ups, downq, downs = sets[i % SETS]
+            assert lib.blk_mlp_forward_fp8(p(x), p(nw), p(upq), p(ups), p(downq), p(downs), p(out), 1, H, I) == 0
+            lib.blk_reset_allocator()
+        for i in range(8):
+            call(i)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = float("inf")
+        for _ in range(3):
+            t0.record()
+            for i in range(CALLS):
+                call(i)
+            t1.record()
+            torch.cuda.synchronize()
+            best = min(best, t0.elapsed_time(t1) * 1e3 / CALLS)
+        us[which] = best
+        lib.blk_free_allocator()
+    ULP_LOG.append(dict(what="latency_us mlp_block_forward_fp8 one token 3136/12544 (reference kernels / this library's ops / fused)",
+                        stock=round(us["stock"], 2), shim=round(us["shim"], 2), fused=round(us["fused"], 2)))
+    assert us["shim"] < us["stock"] and us["fused"] < us["shim"] * 1.1, us
+    assert us["stock"] / us["fused"] > 2.0, us
+
+
 def _mamba_fp8_weights(g):
     inq, ins = fp8_rows(g["in_proj_w"].reshape(MAMBA["PROJ"], 64))
     outq, outs = fp8_rows(g["out_proj_w"].reshape(64, 64))
