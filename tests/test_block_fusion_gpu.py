@@ -289,6 +289,45 @@ def test_single_token_fp8_mlp_block_latency_three_ways(built_lib):
     assert us["stock"] / us["fused"] > 2.0, us
 
 
+def test_prefill_fp8_mlp_block_latency_three_ways(built_lib):
+    """The same block for 4096 tokens: the two FP8 GEMMs (cuBLASLt, the reference's own calls, identical in the three
+    builds) plus what surrounds them - norm, quantise, relu^2, quantise, add: 9 launches of the reference's kernels, or
+    norm + add of this library around the reference's quantisers (shim), or norm+quantise, relu^2+quantise and add in 5
+    launches of this library (fused).  Figures go to the session's report."""
+    from conftest import ULP_LOG
+    M, H, I, CALLS = 4096, 3136, 12544, 12
+    g = torch.Generator().manual_seed(9)
+    nw = (1 + 0.1 * torch.randn(H, generator=g)).cuda()
+    x = torch.randn(M, H, generator=g).to(BF).cuda()
+    upq, ups = fp8_rows(0.02 * torch.randn(I, H, generator=g))
+    downq, downs = fp8_rows(0.02 * torch.randn(H, I, generator=g))
+    out = torch.empty_like(x)
+    us = {}
+    for which in ("stock", "shim", "fused"):
+        lib = load_blocks(which)
+
+        def call():
+            assert lib.blk_mlp_forward_fp8(p(x), p(nw), p(upq), p(ups), p(downq), p(downs), p(out), M, H, I) == 0
+            lib.blk_reset_allocator()
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = float("inf")
+        for _ in range(3):
+            t0.record()
+            for _ in range(CALLS):
+                call()
+            t1.record()
+            torch.cuda.synchronize()
+            best = min(best, t0.elapsed_time(t1) * 1e3 / CALLS)
+        us[which] = best
+        lib.blk_free_allocator()
+    ULP_LOG.append(dict(what="latency_us mlp_block_forward_fp8 4096 tokens 3136/12544 (reference kernels / this library's ops / fused)",
+                        stock=round(us["stock"], 1), shim=round(us["shim"], 1), fused=round(us["fused"], 1)))
+    assert us["fused"] < us["stock"], us
+
+
 def _mamba_fp8_weights(g):
     inq, ins = fp8_rows(g["in_proj_w"].reshape(MAMBA["PROJ"], 64))
     outq, outs = fp8_rows(g["out_proj_w"].reshape(64, 64))
