@@ -248,6 +248,7 @@ def _time_calls(fn, calls, repeats=3):
     return best
 
 
+@pytest.mark.gpu
 def test_fp8_mamba_block_at_model_dimensions_prefill_then_decode(built_lib):
     from conftest import ULP_LOG
     S, HID, H, P, N, CONV = 48, 3136, 96, 80, 128, 9728
@@ -303,6 +304,7 @@ def test_fp8_mamba_block_at_model_dimensions_prefill_then_decode(built_lib):
     assert us["b200"] < us["stock"], us
 
 
+@pytest.mark.gpu
 def test_fp8_attention_block_at_model_dimensions_prefill_then_decode(built_lib):
     from conftest import ULP_LOG
     S, CAP, HID, QD, KD = 64, 128, 3136, 40 * 128, 8 * 128
