@@ -208,10 +208,12 @@ def _mamba_formulation(x, w, S):
     matrices multiplied back by their row scales.  Returns the output rows, the conv window and the SSM state."""
     import torch.nn.functional as F
     nw, inq, ins, cw, cb, A_log, D, dt_bias, gw, outq, outs = w
+    win = inq.float() * ins[:, None] if ins is not None else inq.float()
+    wout = outq.float() * outs[:, None] if outs is not None else outq.float()
     HID, H, P, N, G, INTER, CONV = 3136, 96, 80, 128, 8, 7680, 9728
     xf = x[:S].float()
     normed = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * nw
-    proj = normed @ (inq.float() * ins[:, None]).T
+    proj = normed @ win.T
     gate, xbc, dt = torch.split(proj, [INTER, CONV, H], dim=-1)
     pad = torch.cat([torch.zeros(3, CONV, device=x.device), xbc])
     conv = cb + sum(cw[:, j] * pad[j:j + S] for j in range(4))
@@ -230,7 +232,7 @@ def _mamba_formulation(x, w, S):
     y = torch.stack(ys).reshape(S, INTER) * F.silu(gate)
     yg = y.reshape(S, G, INTER // G)
     y = (yg * torch.rsqrt(yg.pow(2).mean(-1, keepdim=True) + 1e-5)).reshape(S, INTER) * gw
-    out = xf + y @ (outq.float() * outs[:, None]).T
+    out = xf + y @ wout.T
     return out, xbc[S - 3:].T.contiguous(), h
 
 
@@ -350,3 +352,43 @@ def test_fp8_attention_block_at_model_dimensions_prefill_then_decode(built_lib):
     ULP_LOG.append(dict(what="latency_us attention_block_decode_fp8 one token at model dimensions (reference kernels / drop-in fused)",
                         stock=round(us["stock"], 2), fused=round(us["b200"], 2)))
     assert us["b200"] < us["stock"], us
+
+
+@pytest.mark.gpu
+def test_bf16_mamba_block_at_model_dimensions_prefill_then_decode(built_lib):
+    """mamba_forward / mamba_decode of binding.cu:83-105 (bf16 weights) the same way: against the formulation at the
+    reference's bf16 tolerance (max abs error < 0.15, tests/model/test_mamba_block.cu:208,303), states against the stock
+    build, and this library's launches: norm, conv + split, gated norm, add in prefill; the same four with the conv step
+    in decode."""
+    S, HID, H, P, N, CONV, INTER, PROJ = 48, 3136, 96, 80, 128, 9728, 7680, 17504
+    g = torch.Generator(device="cuda").manual_seed(50)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")  # noqa: E731
+    inw, outw = (0.02 * rn(PROJ, HID)).to(BF), (0.02 * rn(HID, INTER)).to(BF)
+    small = [(1 + 0.1 * rn(HID)).contiguous(), (0.3 * rn(CONV, 4)).contiguous(), (0.1 * rn(CONV)).contiguous(),
+             torch.log(1 + 15 * torch.rand(H, generator=g, device="cuda")).contiguous(), (1 + 0.1 * rn(H)).contiguous(),
+             (-3 + 0.5 * rn(H)).contiguous(), (1 + 0.1 * rn(INTER)).contiguous()]
+    nw, cw, cb, A_log, D, dt_bias, gw = small
+    x = rn(S + 1, HID).to(BF)
+    args = [_ptr(nw), _ptr(inw), _ptr(cw), _ptr(cb), _ptr(A_log), _ptr(D), _ptr(dt_bias), _ptr(gw), _ptr(outw)]
+    res = {}
+    for name in ("stock", "b200"):
+        m = load_binding(name)
+        conv_state = torch.zeros(1, CONV, 3, device="cuda")
+        ssm_state = torch.zeros(1, H, P, N, device="cuda")
+        pre = torch.empty(S, HID, dtype=BF, device="cuda")
+        dec = torch.empty(1, HID, dtype=BF, device="cuda")
+        before = built_lib.nmt_launch_count()
+        m.reset_allocator()
+        m.mamba_forward(_ptr(x), *args, _ptr(pre), 1, S, _ptr(conv_state), _ptr(ssm_state))
+        m.reset_allocator()
+        m.mamba_decode(_ptr(x[S:]), *args, _ptr(conv_state), _ptr(ssm_state), _ptr(dec), 1)
+        m.sync()
+        res[name] = (pre, dec, conv_state, ssm_state, built_lib.nmt_launch_count() - before)
+        m.free_allocator()
+    assert res["stock"][4] == 0 and res["b200"][4] == 4 + 4
+    want, want_conv, want_ssm = _mamba_formulation(x, [nw, inw, None, cw, cb, A_log, D, dt_bias, gw, outw, None], S + 1)
+    pre, dec, conv_state, ssm_state = res["b200"][:4]
+    assert (pre.float() - want[:S]).abs().max().item() < 0.15
+    assert (dec[0].float() - want[S]).abs().max().item() < 0.15
+    assert rel_l2(conv_state[0], want_conv) < 0.02 and rel_l2(ssm_state[0], want_ssm) < 0.02
+    assert rel_l2(conv_state, res["stock"][2]) < 1e-2 and rel_l2(ssm_state, res["stock"][3]) < 1e-2
