@@ -1,0 +1,177 @@
+"""One decode step of the whole 42-layer hybrid stack (21 Mamba-2, 17 MLP, 4 attention layers, FP8 weights, the model's
+dimensions of binding.cu:36-45), driven exactly as engine.py:274-289 drives it - embedding, then per layer
+reset_allocator + the block's decode entry of the reference's own pybind module, then the final norm - once on the module
+built on the reference's kernels and once on the drop-in build.  Weights are random (there is no checkpoint here): the
+3.1 GB of e4m3 matrices are read once per step, as in the real model.  The figures go to the session's report; the
+assertions are determinism, finiteness, launch counts and that the drop-in is faster."""
+import pytest
+import torch
+
+from conftest import ULP_LOG
+from nemotron_infer_b200 import chain
+from test_binding_dropin_gpu import _fp8_rows_cuda, _mamba_model_weights, _ptr, load_binding
+
+BF = torch.bfloat16
+HID, INTER, QD, KD, VOCAB = 3136, 12544, 40 * 128, 8 * 128, 8192      # a small table: the gather reads one row per step
+CACHE_CAP, S_CACHE = 1024, 512
+
+
+def _build_layers():
+    g = torch.Generator(device="cuda").manual_seed(77)
+    rn = lambda *s: torch.randn(*s, generator=g, device="cuda")  # noqa: E731
+    layers = []
+    for i, kind in enumerate(chain.layer_schedule()):
+        if kind == "M":
+            layers.append(dict(kind="mamba", w=_mamba_model_weights(1000 + i)))
+        elif kind == "-":
+            up = _fp8_rows_cuda(0.02 * rn(INTER, HID))
+            down = _fp8_rows_cuda(0.02 * rn(HID, INTER))
+            layers.append(dict(kind="mlp", w=[(1 + 0.1 * rn(HID)).contiguous(), *up, *down]))
+        else:
+            w = [(1 + 0.1 * rn(HID)).contiguous()]
+            for rows, cols in ((QD, HID), (KD, HID), (KD, HID), (HID, QD)):
+                w.extend(_fp8_rows_cuda(0.02 * rn(rows, cols)))
+            layers.append(dict(kind="attn", w=w, k0=(0.5 * rn(8, CACHE_CAP, 128)).to(BF), v0=(0.5 * rn(8, CACHE_CAP, 128)).to(BF)))
+    table = (0.02 * rn(VOCAB, HID)).to(BF)
+    norm_f = (1 + 0.1 * rn(HID)).contiguous()
+    return layers, table, norm_f
+
+
+def _fresh_state(layers):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    st = []
+    for ly in layers:
+        if ly["kind"] == "mamba":
+            st.append((0.1 * torch.randn(1, 9728, 3, generator=g, device="cuda"), 0.05 * torch.randn(1, 96, 80, 128, generator=g, device="cuda")))
+        elif ly["kind"] == "attn":
+            st.append((ly["k0"].clone(), ly["v0"].clone()))
+        else:
+            st.append(None)
+    return st
+
+
+def _decode_step(m, layers, state, table, norm_f, ids, bufs, final):
+    cur, other = bufs
+    m.reset_allocator()
+    m.embedding(_ptr(table), _ptr(ids), _ptr(cur), 1)
+    for ly, st in zip(layers, state):
+        m.reset_allocator()
+        w = [_ptr(t) for t in ly["w"]]
+        if ly["kind"] == "mamba":
+            m.mamba_decode_fp8(_ptr(cur), *w, _ptr(st[0]), _ptr(st[1]), _ptr(other), 1)
+        elif ly["kind"] == "attn":
+            m.attn_decode_fp8(_ptr(cur), *w, _ptr(st[0]), _ptr(st[1]), S_CACHE, CACHE_CAP, _ptr(other))
+        else:
+            m.mlp_forward_fp8(_ptr(cur), *w, _ptr(other), 1)
+        cur, other = other, cur
+    m.reset_allocator()
+    m.rmsnorm(_ptr(cur), _ptr(final), _ptr(norm_f), 1)
+
+
+@pytest.mark.gpu
+def test_decode_step_of_the_42_layer_stack_stock_vs_drop_in(built_lib):
+    layers, table, norm_f = _build_layers()
+    ids = torch.tensor([4321], dtype=torch.int64, device="cuda")
+    bufs = (torch.empty(1, HID, dtype=BF, device="cuda"), torch.empty(1, HID, dtype=BF, device="cuda"))
+    us, outs, launches = {}, {}, {}
+    for name in ("stock", "b200"):
+        m = load_binding(name)
+        finals = []
+        for _ in range(2):                                     # same states in, twice: the step is deterministic
+            state = _fresh_state(layers)
+            final = torch.empty(1, HID, dtype=BF, device="cuda")
+            before = built_lib.nmt_launch_count()
+            _decode_step(m, layers, state, table, norm_f, ids, bufs, final)
+            m.sync()
+            launches[name] = built_lib.nmt_launch_count() - before
+            finals.append(final)
+        assert torch.equal(finals[0].view(torch.int16), finals[1].view(torch.int16)), name
+        outs[name] = finals[0]
+        state = _fresh_state(layers)
+        final = torch.empty(1, HID, dtype=BF, device="cuda")
+        for _ in range(3):
+            _decode_step(m, layers, state, table, norm_f, ids, bufs, final)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = float("inf")
+        for _ in range(3):
+            t0.record()
+            for _ in range(10):
+                _decode_step(m, layers, state, table, norm_f, ids, bufs, final)
+            t1.record()
+            torch.cuda.synchronize()
+            best = min(best, t0.elapsed_time(t1) * 1e3 / 10)
+        us[name] = best
+        m.free_allocator()
+    assert torch.isfinite(outs["b200"].float()).all()
+    assert launches["stock"] == 0
+    # gather, 21 x 4 (Mamba-2), 17 x 2 (MLP), 4 x 4 (attention), final norm - against 21 x 12 + 17 x 5 + 4 x 6 + 2 = 363
+    # launches of these ops in the reference's own decode step
+    assert launches["b200"] == 1 + 21 * 4 + 17 * 2 + 4 * 4 + 1
+    ULP_LOG.append(dict(what="latency_us one decode step of the 42-layer FP8 stack at model dimensions, without lm_head (reference kernels / drop-in)",
+                        stock=round(us["stock"], 1), fused=round(us["b200"], 1),
+                        tokens_per_s_stock=round(1e6 / us["stock"], 1), tokens_per_s_fused=round(1e6 / us["b200"], 1)))
+    assert us["b200"] < us["stock"], us
+
+
+def _prefill(m, layers, state, table, norm_f, ids, bufs, final, S):
+    """engine.py:254-272 with cap_states on: every layer's forward entry on all S tokens, states written for decode."""
+    cur, other = bufs
+    m.reset_allocator()
+    m.embedding(_ptr(table), _ptr(ids), _ptr(cur), S)
+    for ly, st in zip(layers, state):
+        m.reset_allocator()
+        w = [_ptr(t) for t in ly["w"]]
+        if ly["kind"] == "mamba":
+            m.mamba_forward_fp8(_ptr(cur), *w, _ptr(other), 1, S, _ptr(st[0]), _ptr(st[1]))
+        elif ly["kind"] == "attn":
+            m.attn_forward_fp8(_ptr(cur), *w, _ptr(other), S, _ptr(st[0]), _ptr(st[1]), CACHE_CAP)
+        else:
+            m.mlp_forward_fp8(_ptr(cur), *w, _ptr(other), S)
+        cur, other = other, cur
+    m.reset_allocator()
+    m.rmsnorm(_ptr(cur), _ptr(final), _ptr(norm_f), S)
+
+
+@pytest.mark.gpu
+def test_prefill_of_the_42_layer_stack_stock_vs_drop_in(built_lib):
+    """The same stack on a 1024-token prompt.  The FP8 GEMMs, the scan and the attention kernels are the reference's in both
+    builds; what differs is every norm, quantiser, conv, activation and residual add around them."""
+    S = 1024
+    layers, table, norm_f = _build_layers()
+    g = torch.Generator(device="cuda").manual_seed(9)
+    ids = torch.randint(0, VOCAB, (S,), generator=g, device="cuda", dtype=torch.int64)
+    bufs = (torch.empty(S, HID, dtype=BF, device="cuda"), torch.empty(S, HID, dtype=BF, device="cuda"))
+    us, launches, outs = {}, {}, {}
+    for name in ("stock", "b200"):
+        m = load_binding(name)
+        state = _fresh_state(layers)
+        final = torch.empty(S, HID, dtype=BF, device="cuda")
+        before = built_lib.nmt_launch_count()
+        _prefill(m, layers, state, table, norm_f, ids, bufs, final, S)
+        m.sync()
+        launches[name] = built_lib.nmt_launch_count() - before
+        outs[name] = final.clone()
+        _prefill(m, layers, state, table, norm_f, ids, bufs, final, S)
+        torch.cuda.synchronize()
+        assert torch.equal(final.view(torch.int16), outs[name].view(torch.int16)), name
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = float("inf")
+        for _ in range(3):
+            t0.record()
+            for _ in range(3):
+                _prefill(m, layers, state, table, norm_f, ids, bufs, final, S)
+            t1.record()
+            torch.cuda.synchronize()
+            best = min(best, t0.elapsed_time(t1) * 1e3 / 3)
+        us[name] = best
+        m.free_allocator()
+    assert torch.isfinite(outs["b200"].float()).all()
+    assert launches["stock"] == 0
+    # gather, 21 x 6 (Mamba-2: norm+quantise 2, conv+split, gated norm+quantise 2, add), 17 x 5 (MLP: norm+quantise 2,
+    # relu^2+quantise 2, add), 4 x 5 (attention: norm+quantise 2, quantiser 2, add), final norm
+    assert launches["b200"] == 1 + 21 * 6 + 17 * 5 + 4 * 5 + 1
+    ULP_LOG.append(dict(what="latency_us prefill of 1024 tokens through the 42-layer FP8 stack at model dimensions, without lm_head (reference kernels / drop-in)",
+                        stock=round(us["stock"], 1), fused=round(us["b200"], 1),
+                        tokens_per_s_stock=round(S * 1e6 / us["stock"], 1), tokens_per_s_fused=round(S * 1e6 / us["b200"], 1)))
+    assert us["b200"] < us["stock"], us
