@@ -199,6 +199,23 @@ int nmt_causal_conv1d_silu_decode_split_bf16(const void* xbc, const float* w, co
                                              void* out2, int64_t n0, int64_t n1, int64_t n2, float* state, int64_t batch,
                                              void* stream);
 
+/* The Mamba-2 state-space recurrence for ONE token per sequence, the step between the conv step and the gated norm
+ * of the decode block (model/mamba_block.cuh:298-301, 499-502).  Replaces the kernel ssm_decode_bf16<H, D, N>
+ * (ops/mamba2/ssm.cuh:43-103, launched there as <<<batch * H, 128>>>), same arguments in the same order:
+ *   dt' = clamp(softplus(dt[h] + dt_bias[h]), dt_min, dt_max),  dA = exp(-exp(A_log[h]) * dt')
+ *   state[b, h, p, n] = state * dA + dt' * B[b, g, n] * x[b, h, p]     (fp32, updated in place)
+ *   y[b, h, p] = sum_n state[b, h, p, n] * C[b, g, n] + D[h] * x[b, h, p],   g = h / (heads / n_groups)
+ * x, y [batch, heads * head_dim] bf16; dt [batch, heads] bf16; B, C [batch, n_groups, state_size] bf16; A_log, D,
+ * dt_bias (may be NULL) [heads] fp32; state [batch, heads, head_dim, state_size] fp32.  state_size <= 256.
+ * State and y are bit-identical to the reference kernel's (same element-to-lane assignment, same reduction tree).
+ * The state rows are requested before the kernel waits for its predecessor on the stream: that predecessor must
+ * not be the one that writes `state` (in the decode block it is the conv step; the state's only writer is this
+ * entry point one token earlier). */
+int nmt_ssm_decode_step_bf16(const void* x, const void* dt, const float* A_log, const void* B, const void* C,
+                             const float* D, const float* dt_bias, float* state, void* y, int64_t batch, int64_t heads,
+                             int64_t head_dim, int64_t state_size, int64_t n_groups, float dt_min, float dt_max,
+                             void* stream);
+
 /* fp32 twin, unsplit; replaces causal_conv1d_prefill_fp32 (ops/mamba2/causal_conv1d.cuh:115-127). */
 int nmt_causal_conv1d_silu_f32(const float* x, const float* w, const float* bias, float* y, float* state_out,
                                int64_t conv_dim, int64_t S, int64_t batch, void* stream);

@@ -16,11 +16,13 @@
 //                              entry point each (:140+158, :163+167); single token: norm + up_proj + relu^2 is one
 //                              launch, down_proj + residual add another (:140-148, :170-173) - 2 launches for 5
 //   mamba_block_forward_bf16   (model/mamba_block.cuh:149-227) conv1d + SiLU writes x | B | C directly (:195-207)
-//   mamba_block_decode_bf16    (model/mamba_block.cuh:238-311) the same for the single-token conv step (:281-293)
+//   mamba_block_decode_bf16    (model/mamba_block.cuh:238-311) the same for the single-token conv step (:281-293); the
+//                              state-space step on nmt_ssm_decode_step_bf16 (:298-301)
 //   mamba_block_forward_fp8    (model/mamba_block.cuh:336-429) norm -> quantise (:378-381), conv + split (:394-406),
 //                              gated norm -> quantise (:415-420)
 //   mamba_block_decode_fp8     (model/mamba_block.cuh:439-516) norm + the three in_proj slices in one launch
-//                              (:473-481), conv step + split (:484-496), out_proj + residual add (:508-514) -
+//                              (:473-481), conv step + split (:484-496), the state-space step on
+//                              nmt_ssm_decode_step_bf16 (:499-502), out_proj + residual add (:508-514) -
 //                              5 launches for 12
 //   attention_block_forward_fp8 (model/attention_block.cuh:286-358) norm -> quantise in one entry point (:328-330)
 //   attention_block_decode_fp8  (model/attention_block.cuh:363-414) the pre-norm inside each of the q / k / v GEMVs
@@ -192,8 +194,8 @@ inline void mamba_block_decode_bf16(const __nv_bfloat16* input, const Mamba2Bloc
         ops::gemm_bf16(normed, w.in_proj_w + static_cast<size_t>(INTER + CONV_DIM) * HIDDEN, dt, B, H, HIDDEN, stream);
         ok(nmt_causal_conv1d_silu_decode_split_bf16(xbc, w.conv1d_w, w.conv1d_b, x, Bm, Cm, INTER, GN, GN, conv_state, B, stream),
            "nmt_causal_conv1d_silu_decode_split_bf16");
-        ops::mamba2::ssm_decode_bf16<H, P, N><<<dim3(B * H), 128, 0, stream>>>(x, dt, w.A_log, Bm, Cm, w.D, ssm_state, y, w.dt_bias,
-                                                                                B, G, 0.f, FLT_MAX);
+        ok(nmt_ssm_decode_step_bf16(x, dt, w.A_log, Bm, Cm, w.D, w.dt_bias, ssm_state, y, B, H, P, N, G, 0.f, FLT_MAX, stream),
+           "nmt_ssm_decode_step_bf16");
         ops::rmsnorm_gated_bf16<G>(y, gnormed, w.gnorm_w, gate, B, INTER, INTER / G, EPS, stream);
         ops::gemm_bf16(gnormed, w.out_proj_w, mixer, B, HIDDEN, INTER, stream);
         ops::elementwise_ops_bf16<ops::kElementwiseAdd>(input, mixer, out, rows * HIDDEN, 1.f, nullptr, 0.f, 1.f, stream);
@@ -268,8 +270,8 @@ inline void mamba_block_decode_fp8(const __nv_bfloat16* input, const Mamba2Block
            "nmt_gemv_w8a16_fused(norm, in_proj)");
         ok(nmt_causal_conv1d_silu_decode_split_bf16(xbc, w.conv1d_w, w.conv1d_b, x, Bm, Cm, INTER, GN, GN, conv_state, 1, stream),
            "nmt_causal_conv1d_silu_decode_split_bf16");
-        ops::mamba2::ssm_decode_bf16<H, P, N><<<dim3(H), 128, 0, stream>>>(x, dt, w.A_log, Bm, Cm, w.D, ssm_state, y, w.dt_bias, 1, G,
-                                                                            0.f, FLT_MAX);
+        ok(nmt_ssm_decode_step_bf16(x, dt, w.A_log, Bm, Cm, w.D, w.dt_bias, ssm_state, y, 1, H, P, N, G, 0.f, FLT_MAX, stream),
+           "nmt_ssm_decode_step_bf16");
         ops::rmsnorm_gated_bf16<G>(y, gnormed, w.gnorm_w, gate, 1, INTER, INTER / G, EPS, stream);
         ok(nmt_gemv_w8a16_fused(gnormed, nullptr, 0.f, w.out_proj_w, w.out_proj_wscale, 0, input, out, HIDDEN, INTER, stream),
            "nmt_gemv_w8a16_fused(out_proj, residual)");

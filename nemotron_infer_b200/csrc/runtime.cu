@@ -25,6 +25,7 @@ int finish_launch(int n_kernels) {
 // Knobs are plain ints read at launch time.  0 means "let the launcher decide".
 struct Knob { const char* key; std::atomic<int> value; };
 static Knob g_knobs[] = {
+    {"ssm.rows_per_warp", {0}},   // SSM decode step: rows of a head a warp handles together (1, 2, 4 or 5; default: by rows per head)
     {"launch.pdl", {0}},          // 1 = launch with programmatic stream serialization (default), 2 = plain launches
     // add_rmsnorm / rmsnorm (bf16)
     {"norm.cluster", {0}},        // RMSNorm: 0 = cluster of CTAs per row only for rows one CTA cannot hold, 2/4/8 = always, 1 = never

@@ -43,6 +43,7 @@ SHAPES = {
     # single-token decode projections (weight streaming): "tokens" is the number of output rows N here
     "gemv_up": (12544, 3136),        # up_proj   N = 12544, K = 3136: 3136 weight bytes per output row
     "gemv_down": (3136, 12544),      # down_proj N = 3136,  K = 12544
+    "ssm_step": (1, 2 * 96 * 80 * 128 * 4),   # per sequence: the fp32 state [96, 80, 128] read and written once
     # e4m3 activation quantisation (the step after the norm / activation in the FP8 blocks)
     "quantize_fp8": (8192, 3136 * (2 + 2 + 1)),                  # amax pass + quantising pass over [T, 3136]
     "add_rmsnorm_quant_fp8": (8192, 3136 * (2 + 2 + 2 + 2 + 1)),  # x, r -> out_res ; out_res -> e4m3
@@ -88,6 +89,14 @@ def make_case(op: str, T: int, dev):
         sc = torch.rand(T, device=dev) * 0.01
         y = torch.empty(T, dtype=BF, device=dev)
         return lambda: ops.gemv_w8a16(x, W, sc, out=y)
+    if op == "ssm_step":
+        H, P, N, G = 96, 80, 128, 8
+        x, dt = rn(T, H * P).to(BF), (rn(T, H) - 1).to(BF)
+        A_log, D, bias = torch.log(1 + 15 * torch.rand(H, device=dev)), 1 + 0.1 * rn(H), 0.5 * rn(H)
+        Bm, Cm = rn(T, G, N).to(BF), rn(T, G, N).to(BF)
+        state = 0.3 * rn(T, H, P, N)
+        y = torch.empty(T, H * P, dtype=BF, device=dev)
+        return lambda: ops.ssm_decode_step(x, dt, A_log, Bm, Cm, D, state, dt_bias=bias, out=y)
     if op == "conv1d_split":
         xbc = rn(1, T, 9728).to(BF)
         w, b = 0.2 * rn(9728, 4), 0.1 * rn(9728)
@@ -125,7 +134,11 @@ def make_case(op: str, T: int, dev):
 def run_op(op: str, T: int, reps: int, warmup: int, dev, batch: int = 10, graph: bool = False) -> dict:
     _, bpt = SHAPES[op]
     nbytes = bpt * T
-    nsets = max(2, min(8, -(-2 * L2_BYTES // max(nbytes, 1)) + 1))
+    # enough buffer sets that a launch never finds its tensors in L2 (at most 8; the small per-sequence state of the SSM
+    # step, which in a decode step is evicted by 3 GB of weights between two uses, gets as many as that takes)
+    nsets = max(2, min(48 if op == "ssm_step" else 8, -(-2 * L2_BYTES // max(nbytes, 1)) + 1))
+    if op == "ssm_step":
+        batch = max(batch, nsets)                 # one timed interval walks every set once
     fns = [make_case(op, T, dev) for _ in range(nsets)]
     for i in range(max(warmup, 3)):
         fns[i % nsets]()
@@ -231,7 +244,7 @@ def main() -> None:
             print(json.dumps(run_fixed_cost(op, T, a.reps, f"cuda:{a.device}")), flush=True)
             torch.cuda.empty_cache()
             continue
-        print(json.dumps(run_op(op, T, a.reps, a.warmup, f"cuda:{a.device}", a.batch, a.graph or op.startswith("gemv"))), flush=True)
+        print(json.dumps(run_op(op, T, a.reps, a.warmup, f"cuda:{a.device}", a.batch, a.graph or op.startswith("gemv") or op == "ssm_step")), flush=True)
         torch.cuda.empty_cache()
 
 

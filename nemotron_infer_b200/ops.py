@@ -211,6 +211,26 @@ def causal_conv1d_silu_decode(xbc: torch.Tensor, w: torch.Tensor, bias: torch.Te
     return outs if split is not None else outs[0]
 
 
+def ssm_decode_step(x: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, B: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
+                    state: torch.Tensor, dt_bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                    dt_min: float = 0.0, dt_max: float = 3.4028234663852886e38) -> torch.Tensor:
+    """One token of the Mamba-2 recurrence: updates `state` [batch, H, P, N] (fp32) in place and returns y [batch, H * P]
+    (bf16).  x [batch, H * P], dt [batch, H], B and C [batch, G, N] are bf16; A_log, D, dt_bias [H] fp32."""
+    batch, H, P, N = state.shape
+    G = B.shape[-2]
+    out = torch.empty(batch, H * P, dtype=torch.bfloat16, device=x.device) if out is None else out
+    _dev(x, dt, A_log, B, C, D, state, out)
+    if any(t.dtype != torch.bfloat16 for t in (x, dt, B, C, out)) or any(t.dtype != torch.float32 for t in (A_log, D, state)):
+        raise ValueError("x, dt, B, C, out must be bf16; A_log, D, state fp32")
+    if x.numel() != batch * H * P or dt.numel() != batch * H or B.numel() != batch * G * N or C.numel() != batch * G * N:
+        raise ValueError("shape mismatch")
+    _lib.check(_lib.load().nmt_ssm_decode_step_bf16(x.data_ptr(), dt.data_ptr(), A_log.data_ptr(), B.data_ptr(), C.data_ptr(),
+                                                    D.data_ptr(), dt_bias.data_ptr() if dt_bias is not None else None,
+                                                    state.data_ptr(), out.data_ptr(), batch, H, P, N, G, float(dt_min), float(dt_max),
+                                                    _stream()), "ssm_decode_step")
+    return out
+
+
 def gemv_w8a16(x: torch.Tensor, W: torch.Tensor, w_scale: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """y[N] = (W[N, K] (e4m3) @ x[K] (bf16)) * w_scale[N], fp32 accumulation, bf16 result: the decode projection."""
     N, K = W.shape

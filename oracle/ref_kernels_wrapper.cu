@@ -5,6 +5,7 @@
 // time "the reference kernels recompiled for sm_100a" beside the new kernels.
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cfloat>
 #include <cstdint>
 
 #include "tensor/tensor.h"
@@ -13,6 +14,7 @@
 #include "ops/embedding.cuh"     // embedding_lookup<Hidden>
 #include "ops/gemv.cuh"                   // gemv_fp8
 #include "ops/mamba2/causal_conv1d.cuh"   // causal_conv1d_prefill_{fp32,bf16}
+#include "ops/mamba2/ssm.cuh"             // ssm_decode_bf16<H, D, N>
 
 using namespace nemotron::ops;
 using bf16 = __nv_bfloat16;
@@ -113,3 +115,22 @@ REF_API int ref_gemv_fp8(const void* x, const void* W, const float* w_scale, voi
 }
 
 REF_API int ref_set_device(int d) { return static_cast<int>(cudaSetDevice(d)); }
+
+// The single-token SSM step at the model's dimensions and at those of the reference's dump script, launched as the
+// decode blocks launch it (model/mamba_block.cuh:298-301).
+REF_API int ref_ssm_decode_bf16(const void* x, const void* dt, const float* A_log, const void* B, const void* C, const float* D,
+                                const float* dt_bias, float* state, void* y, int batch, int H, int P, int N, int groups, void* st) {
+    auto X = static_cast<const bf16*>(x);
+    auto DT = static_cast<const bf16*>(dt);
+    auto Bp = static_cast<const bf16*>(B);
+    auto Cp = static_cast<const bf16*>(C);
+    auto Y = static_cast<bf16*>(y);
+    cudaStream_t s = static_cast<cudaStream_t>(st);
+    if (H == 96 && P == 80 && N == 128)
+        mamba2::ssm_decode_bf16<96, 80, 128><<<dim3(batch * H), 128, 0, s>>>(X, DT, A_log, Bp, Cp, D, state, Y, dt_bias, batch, groups, 0.f, FLT_MAX);
+    else if (H == 4 && P == 16 && N == 16)
+        mamba2::ssm_decode_bf16<4, 16, 16><<<dim3(batch * H), 128, 0, s>>>(X, DT, A_log, Bp, Cp, D, state, Y, dt_bias, batch, groups, 0.f, FLT_MAX);
+    else
+        return -1;
+    return last();
+}

@@ -129,6 +129,24 @@ def causal_conv1d_decode_bf16(x_t: torch.Tensor, w: torch.Tensor, b: torch.Tenso
     return F.silu(acc).to(torch.bfloat16), new_state
 
 
+def ssm_decode_step(x: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, B: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
+                    state: torch.Tensor, dt_bias: torch.Tensor | None = None):
+    """One token of the Mamba-2 recurrence in the arithmetic of ops/mamba2/ssm.cuh:43-103 (fp32 throughout): x [H, P],
+    dt [H], B and C [G, N], state [H, P, N]; consecutive heads share a B / C group (h -> h // (H / G), the convention
+    tools/dump_mamba_block.py:140-145 states).  Returns (y [H, P] fp32 before rounding, new state)."""
+    H, P, N = state.shape
+    G = B.shape[0]
+    dtv = dt.float() + (dt_bias.float() if dt_bias is not None else 0.0)
+    dtv = torch.where(dtv > 20.0, dtv, torch.where(dtv < -20.0, torch.zeros_like(dtv), torch.log1p(torch.exp(dtv))))
+    dA = torch.exp(-torch.exp(A_log.float()) * dtv)
+    Bh = B.float().repeat_interleave(H // G, dim=0)
+    Ch = C.float().repeat_interleave(H // G, dim=0)
+    xf = x.float()
+    new = state.float() * dA[:, None, None] + (dtv[:, None] * xf)[:, :, None] * Bh[:, None, :]
+    y = (new * Ch[:, None, :]).sum(-1) + D.float()[:, None] * xf
+    return y, new
+
+
 def quant_weight_perrow(Wf: torch.Tensor):
     """Per-output-row e4m3 quantisation of an fp32 weight matrix: (W_e4m3, w_scale)."""
     amax = Wf.abs().amax(dim=1)

@@ -375,8 +375,9 @@ def test_mamba_prefill_then_decode_bf16(built_lib, which):
     assert (pre.float() - want[:MAMBA["S"] - 1]).abs().max().item() < 1.5e-1
     # the conv window after the decode step holds the last three raw xBC rows; finite and changed by the step
     assert torch.isfinite(conv_state).all()
-    # norm, gated norm, add per block call; the fused forms add the split-fused conv (prefill) and conv step (decode)
-    assert launched == (6 if which == "shim" else 8)
+    # norm, gated norm, add per block call; the fused forms add the split-fused conv (prefill), the conv step and the
+    # state-space step (decode)
+    assert launched == (6 if which == "shim" else 9)
 
 
 @pytest.mark.parametrize("which", ["shim", "fused"])
@@ -393,8 +394,8 @@ def test_mamba_prefill_then_decode_fp8(built_lib, which):
         assert launched == 3 + 7
     else:
         # prefill: norm+quant (2), conv+split, gated norm with maximum + quantiser (2), add; decode: norm+in_proj GEMV,
-        # conv step, gated norm, out_proj GEMV + add
-        assert launched == 6 + 4
+        # conv step, state-space step, gated norm, out_proj GEMV + add
+        assert launched == 6 + 5
 
 
 def test_mamba_fp8_decode_fused_equals_unfused_bit_for_bit(built_lib):

@@ -134,3 +134,24 @@ def test_c_embedding_loop(oracle_c):
                                ids.ctypes.data_as(ctypes.POINTER(ctypes.c_int64)),
                                out.ctypes.data_as(ctypes.POINTER(ctypes.c_uint16)), ids.size, table.shape[1])
     np.testing.assert_array_equal(out, d["cfg4_out"])
+
+
+def test_ssm_decode_step_iterated_reproduces_the_dump_scripts_scan():
+    """The single-token recurrence (oracle of ops/mamba2/ssm.cuh:43-103), stepped over the 24 tokens of
+    tools/dump_mamba_block.py from a zero state, must give the chunked scan's output `scan_y` of that script: x, B, C from
+    its `xbc_conv`, dt from its `normed` and `in_proj_w` (the last H rows), A_log / D / dt_bias as dumped."""
+    d = golden("dump_mamba_block.npz")
+    H, P, N, G, S, INTER, CONV, HID = 4, 16, 16, 2, 24, 64, 128, 64
+    f = lambda k, *shape: torch.from_numpy(d[k].copy()).reshape(*shape)  # noqa: E731
+    conv = f("xbc_conv", S, CONV)
+    proj_dt = f("normed", S, HID) @ f("in_proj_w", INTER + CONV + H, HID)[INTER + CONV:].T
+    A_log, D, dt_bias = f("A_log", H), f("D", H), f("dt_bias", H)
+    state = torch.zeros(H, P, N)
+    ys = []
+    for t in range(S):
+        x, B, C = conv[t, :INTER].reshape(H, P), conv[t, INTER:INTER + G * N].reshape(G, N), conv[t, INTER + G * N:].reshape(G, N)
+        y, state = og.ssm_decode_step(x, proj_dt[t], A_log, B, C, D, state, dt_bias)
+        ys.append(y.reshape(INTER))
+    got = torch.stack(ys)
+    want = f("scan_y", S, INTER)
+    assert (got - want).abs().max().item() < 2e-4 * max(1.0, want.abs().max().item())
