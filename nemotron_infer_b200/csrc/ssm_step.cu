@@ -9,8 +9,8 @@
 // else is a few KB.  The reference gives a head to a 128-thread CTA whose four warps walk the head's P rows one after
 // the other (96 CTAs, 20 dependent rows per warp).  Here a head is split over five 8-warp CTAs and a warp requests all
 // the elements of its two rows before it uses the first (the whole state of a sequence in flight at once), while the
-// per-head scalars (softplus, two exponentials) and the head's B / C values are computed and loaded once per warp, not
-// once per row: with only four state elements per lane and row they would otherwise be most of the instructions.  A
+// per-head scalars (softplus, two exponentials) are computed once per CTA and the head's B / C values loaded once per
+// warp, not once per row: with only four state elements per lane and row they would otherwise be most of the instructions.  A
 // lane owns the same elements n = lane, lane + 32, ... of a row as in the reference and the row sum goes down the same
 // shuffle tree, so state and y are bit-identical to the reference kernel's.
 //
@@ -27,13 +27,15 @@ __global__ void __launch_bounds__(kSsmWarps * 32)
 ssm_step_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dt, const float* __restrict__ A_log,
                 const __nv_bfloat16* __restrict__ B, const __nv_bfloat16* __restrict__ C, const float* __restrict__ D_param,
                 const float* __restrict__ dt_bias, float* __restrict__ state, __nv_bfloat16* __restrict__ y,
-                int H, int P, int N, int groups, int chunks, float dt_min, float dt_max) {
+                int H, int P, int N, int groups, float dt_min, float dt_max) {
     const int lane = threadIdx.x & 31;
     // A CTA owns kSsmWarps * RPW consecutive rows p of one (sequence, head); a warp RPW of them.  All of a warp's state
-    // elements are requested before the first use; the per-head scalars and the head's B / C values are computed and
-    // loaded once per warp.
-    const int bh = blockIdx.x / chunks;                            // sequence * H + head
-    const int p0 = ((blockIdx.x % chunks) * kSsmWarps + (threadIdx.x >> 5)) * RPW;
+    // elements are requested before the first use; the per-head scalars are computed by one thread of the CTA, the
+    // head's B / C values loaded once per warp.
+    __shared__ float s_scalar[3];
+    __shared__ int s_bc;
+    const int bh = blockIdx.x;                                     // sequence * H + head
+    const int p0 = (blockIdx.y * kSsmWarps + (threadIdx.x >> 5)) * RPW;
     float* s_base = state + ((int64_t)bh * P + min(p0, P - 1)) * N;
     float s[RPW][NPER];
 #pragma unroll
@@ -45,18 +47,23 @@ ssm_step_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
         }
     }
     pdl_wait();
-    if (p0 < P) {                                                  // warp-uniform
+    if (threadIdx.x == 0) {
         const int h = bh % H, b = bh / H;
-        const int group = h / (H / groups);
         // softplus and the decay exactly as the reference writes them (ops/mamba2/ssm.cuh:72-79)
         float dt_v = __bfloat162float(dt[bh]);
         if (dt_bias) dt_v += dt_bias[h];
         const float sp = (dt_v > 20.f) ? dt_v : (dt_v < -20.f) ? 0.f : logf(1.f + expf(dt_v));
         dt_v = fminf(dt_max, fmaxf(dt_min, sp));
-        const float dA = expf(-expf(A_log[h]) * dt_v);
-        const float Dh = D_param[h];
-        const __nv_bfloat16* Bg = B + (int64_t)(b * groups + group) * N;
-        const __nv_bfloat16* Cg = C + (int64_t)(b * groups + group) * N;
+        s_scalar[0] = dt_v;
+        s_scalar[1] = expf(-expf(A_log[h]) * dt_v);
+        s_scalar[2] = D_param[h];
+        s_bc = b * groups + h / (H / groups);                      // which [N] row of B and C this head reads
+    }
+    __syncthreads();
+    if (p0 < P) {                                                  // warp-uniform
+        const float dt_v = s_scalar[0], dA = s_scalar[1], Dh = s_scalar[2];
+        const __nv_bfloat16* Bg = B + (int64_t)s_bc * N;
+        const __nv_bfloat16* Cg = C + (int64_t)s_bc * N;
         float dtB[NPER], sC[NPER];
 #pragma unroll
         for (int j = 0; j < NPER; ++j) {
@@ -119,18 +126,25 @@ int nmt_ssm_decode_step_bf16(const void* x, const void* dt, const float* A_log, 
         }
     }
     const int64_t chunks = (head_dim + (int64_t)kSsmWarps * rpw - 1) / ((int64_t)kSsmWarps * rpw);
-    const int64_t grid = batch * heads * chunks;
-    if (grid > 0x7fffffff || batch * heads * head_dim > 0x7fffffff) return NMT_ERR_UNSUPPORTED;
+    if (batch * heads > 0x7fffffff || chunks > 65535 || batch * heads * head_dim > 0x7fffffff) return NMT_ERR_UNSUPPORTED;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     auto X = static_cast<const __nv_bfloat16*>(x);
     auto DT = static_cast<const __nv_bfloat16*>(dt);
     auto Bp = static_cast<const __nv_bfloat16*>(B);
     auto Cp = static_cast<const __nv_bfloat16*>(C);
     auto Y = static_cast<__nv_bfloat16*>(y);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(batch * heads), static_cast<unsigned>(chunks));
+    cfg.blockDim = dim3(kSsmWarps * 32);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
 #define NMT_SSM_LAUNCH(NP, RW)                                                                                              \
-    launch_kernel(ssm_step_kernel<NP, RW>, static_cast<int>(grid), kSsmWarps * 32, 0, st, X, DT, A_log, Bp, Cp, D, dt_bias, state, Y, \
-                  static_cast<int>(heads), static_cast<int>(head_dim), static_cast<int>(state_size), static_cast<int>(n_groups),       \
-                  static_cast<int>(chunks), dt_min, dt_max)
+    cudaLaunchKernelEx(&cfg, ssm_step_kernel<NP, RW>, X, DT, A_log, Bp, Cp, D, dt_bias, state, Y, static_cast<int>(heads),   \
+                       static_cast<int>(head_dim), static_cast<int>(state_size), static_cast<int>(n_groups), dt_min, dt_max)
 #define NMT_SSM_CASE(NP)                                                                                                    \
     do {                                                                                                                    \
         if (rpw == 5) NMT_SSM_LAUNCH(NP, 5); else if (rpw == 4) NMT_SSM_LAUNCH(NP, 4);                                      \
