@@ -216,6 +216,23 @@ int nmt_ssm_decode_step_bf16(const void* x, const void* dt, const float* A_log, 
                              int64_t head_dim, int64_t state_size, int64_t n_groups, float dt_min, float dt_max,
                              void* stream);
 
+/* Attention for ONE query token per call over the KV cache, the decode step of the attention block
+ * (model/attention_block.cuh:249-253, 403-406).  Replaces sdpa_decode_bf16<128> (ops/attention/sdpa_decode.cuh:
+ * 275-291: its split kernel :56-122, combine kernel :127-186 and the process-wide scratch :192-221), same arguments
+ * plus the workspace:
+ *   O[h] = sum_{s < S_cache} softmax_s(Q[h] . K_cache[g, s] / sqrt(128)) V_cache[g, s],   g = h / (heads / kv_heads),
+ *   then K_new / V_new [kv_heads, 128] are written to position S_cache of the caches [kv_heads, total_S, 128] - the
+ *   new token does not attend to itself, exactly as in the reference.  S_cache == 0 gives O = 0.
+ * All tensors bf16; Q and O [heads, 128]; fp32 accumulation; results agree with the reference kernel to bf16
+ * rounding (the positions are split differently, so the fp32 sums associate differently).  head_dim must be 128 and
+ * heads / kv_heads one of 1, 2, 4, 5, 8 (NMT_ERR_UNSUPPORTED otherwise).  workspace: nmt_sdpa_decode_workspace_bytes(
+ * S_cache, heads) bytes of device memory, 16-byte aligned, contents need no initialisation.  Q, the caches 8-byte
+ * aligned.  Two launches. */
+int64_t nmt_sdpa_decode_workspace_bytes(int64_t S_cache, int64_t num_heads);
+int nmt_sdpa_decode_bf16(const void* Q, void* K_cache, void* V_cache, void* O, const void* K_new, const void* V_new,
+                         int64_t S_cache, int64_t total_S, int64_t num_heads, int64_t num_kv_heads, int64_t head_dim,
+                         void* workspace, void* stream);
+
 /* fp32 twin, unsplit; replaces causal_conv1d_prefill_fp32 (ops/mamba2/causal_conv1d.cuh:115-127). */
 int nmt_causal_conv1d_silu_f32(const float* x, const float* w, const float* bias, float* y, float* state_out,
                                int64_t conv_dim, int64_t S, int64_t batch, void* stream);

@@ -28,6 +28,8 @@
 //   attention_block_decode_fp8  (model/attention_block.cuh:363-414) the pre-norm inside each of the q / k / v GEMVs
 //                              (:396-401), o_proj + residual add in one launch (:408-413) - 4 launches of this
 //                              library for 6
+//   - nemotron::ops::attention::sdpa_decode_bf16 (ops/attention/sdpa_decode.cuh:275-291), called by both decode forms
+//     of the attention block (model/attention_block.cuh:251, 405), forwards to nmt_sdpa_decode_bf16;
 // Every fused form returns what the reference's sequence of this library's single ops returns, byte for byte
 // (the entry points are tested for exactly that), so swapping a block changes its traffic, not its numbers.
 #ifndef NEMOTRON_B200_SHIM_BLOCKS_CUH
@@ -55,7 +57,12 @@ inline void quantize_activation_fp8(const __nv_bfloat16* x_bf16, __nv_fp8_e4m3* 
 }
 }  // namespace nemotron::ops
 
-// -- the reference's blocks; the five that get a fused form keep their bodies under *_reference -------------------
+// -- the reference's decode attention under another name, ours under its name (defined after the allocator) -----
+#define sdpa_decode_bf16 sdpa_decode_bf16_reference
+#include "ops/attention/sdpa_decode.cuh"
+#undef sdpa_decode_bf16
+
+// -- the reference's blocks; the seven that get a fused form keep their bodies under *_reference ------------------
 #define mlp_block_forward_fp8 mlp_block_forward_fp8_reference
 #define mamba_block_forward_bf16 mamba_block_forward_bf16_reference
 #define mamba_block_decode_bf16 mamba_block_decode_bf16_reference
@@ -65,6 +72,25 @@ inline void quantize_activation_fp8(const __nv_bfloat16* x_bf16, __nv_fp8_e4m3* 
 #define attention_block_decode_fp8 attention_block_decode_fp8_reference
 #include "tensor/tensor.h"
 #include "tensor/allocator.cuh"
+
+namespace nemotron::ops::attention {
+// ops/attention/sdpa_decode.cuh:275-291, same arguments.  The partial results of the splits live in a transient tensor
+// of the caller's bump allocator (the reference keeps a process-wide cudaMalloc'd scratch for them, :192-221).
+template <int HEAD = 128>
+inline void sdpa_decode_bf16(const __nv_bfloat16* Q, __nv_bfloat16* K_cache, __nv_bfloat16* V_cache, __nv_bfloat16* O,
+                             const __nv_bfloat16* K_new, const __nv_bfloat16* V_new, const int S_cache, const int total_S,
+                             const int num_heads, int num_kv_heads = -1, cudaStream_t stream = nullptr) {
+    if (num_heads == 0) return;
+    if (num_kv_heads <= 0) num_kv_heads = num_heads;
+    const int64_t bytes = nmt_sdpa_decode_workspace_bytes(S_cache, num_heads);
+    void* ws = bytes > 0 ? nemotron::allocate_tensor<float>(nemotron::TensorShape::make_1d(bytes / 4)).data_ : nullptr;
+    const int s = nmt_sdpa_decode_bf16(Q, K_cache, V_cache, O, K_new, V_new, S_cache, total_S, num_heads, num_kv_heads, HEAD, ws, stream);
+    if (s == NMT_ERR_UNSUPPORTED)                                  // a head size or group ratio this library has no kernel for
+        return sdpa_decode_bf16_reference<HEAD>(Q, K_cache, V_cache, O, K_new, V_new, S_cache, total_S, num_heads, num_kv_heads, stream);
+    nemotron::ops::detail::nmt_shim_check(s, "nmt_sdpa_decode_bf16");
+}
+}  // namespace nemotron::ops::attention
+
 #include "model/mlp_block.cuh"
 #include "model/mamba_block.cuh"
 #include "model/attention_block.cuh"

@@ -211,6 +211,27 @@ def causal_conv1d_silu_decode(xbc: torch.Tensor, w: torch.Tensor, bias: torch.Te
     return outs if split is not None else outs[0]
 
 
+def sdpa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
+                s_cache: int, out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """Attention of one query token [H_Q, 128] over the first `s_cache` positions of the caches [H_KV, cap, 128]; then
+    k_new / v_new [H_KV, 128] are written to position `s_cache` (the new token does not attend to itself)."""
+    H_Q, D = q.shape
+    H_KV, cap, _ = k_cache.shape
+    out = torch.empty_like(q) if out is None else out
+    _dev(q, k_cache, v_cache, k_new, v_new, out)
+    if any(t.dtype != torch.bfloat16 for t in (q, k_cache, v_cache, k_new, v_new, out)):
+        raise ValueError("all tensors must be bf16")
+    lib = _lib.load()
+    need = lib.nmt_sdpa_decode_workspace_bytes(int(s_cache), H_Q)
+    if workspace is None:
+        workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    elif workspace.numel() * workspace.element_size() < need:
+        raise ValueError("workspace too small")
+    _lib.check(lib.nmt_sdpa_decode_bf16(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), k_new.data_ptr(),
+                                        v_new.data_ptr(), int(s_cache), cap, H_Q, H_KV, D, workspace.data_ptr(), _stream()), "sdpa_decode")
+    return out
+
+
 def ssm_decode_step(x: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, B: torch.Tensor, C: torch.Tensor, D: torch.Tensor,
                     state: torch.Tensor, dt_bias: torch.Tensor | None = None, out: torch.Tensor | None = None,
                     dt_min: float = 0.0, dt_max: float = 3.4028234663852886e38) -> torch.Tensor:

@@ -15,6 +15,7 @@
 #include "ops/gemv.cuh"                   // gemv_fp8
 #include "ops/mamba2/causal_conv1d.cuh"   // causal_conv1d_prefill_{fp32,bf16}
 #include "ops/mamba2/ssm.cuh"             // ssm_decode_bf16<H, D, N>
+#include "ops/attention/sdpa_decode.cuh"  // sdpa_decode_bf16<HEAD>
 
 using namespace nemotron::ops;
 using bf16 = __nv_bfloat16;
@@ -132,5 +133,14 @@ REF_API int ref_ssm_decode_bf16(const void* x, const void* dt, const float* A_lo
         mamba2::ssm_decode_bf16<4, 16, 16><<<dim3(batch * H), 128, 0, s>>>(X, DT, A_log, Bp, Cp, D, state, Y, dt_bias, batch, groups, 0.f, FLT_MAX);
     else
         return -1;
+    return last();
+}
+
+// Decode attention as the attention blocks call it (model/attention_block.cuh:251); its scratch is the reference's own.
+REF_API int ref_sdpa_decode_bf16(const void* Q, void* K_cache, void* V_cache, void* O, const void* K_new, const void* V_new,
+                                 int S_cache, int total_S, int num_heads, int num_kv_heads, void* st) {
+    attention::sdpa_decode_bf16<128>(static_cast<const bf16*>(Q), static_cast<bf16*>(K_cache), static_cast<bf16*>(V_cache),
+                                     static_cast<bf16*>(O), static_cast<const bf16*>(K_new), static_cast<const bf16*>(V_new), S_cache,
+                                     total_S, num_heads, num_kv_heads, static_cast<cudaStream_t>(st));
     return last();
 }

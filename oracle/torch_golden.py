@@ -147,6 +147,21 @@ def ssm_decode_step(x: torch.Tensor, dt: torch.Tensor, A_log: torch.Tensor, B: t
     return y, new
 
 
+def sdpa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, s_cache: int) -> torch.Tensor:
+    """One query token over the first s_cache cached positions, the formulation of tools/dump_attention_block.py
+    (softmax(q K^T / sqrt(d)) V with consecutive query heads sharing a KV head) restricted to what the decode kernel of
+    ops/attention/sdpa_decode.cuh:98-115 covers: positions [0, s_cache), the new token not included.  fp32; q [H_Q, D],
+    caches [H_KV, cap, D]."""
+    H_Q, D = q.shape
+    H_KV = k_cache.shape[0]
+    if s_cache == 0:
+        return torch.zeros(H_Q, D)
+    K = k_cache[:, :s_cache].float().repeat_interleave(H_Q // H_KV, dim=0)      # [H_Q, s, D]
+    V = v_cache[:, :s_cache].float().repeat_interleave(H_Q // H_KV, dim=0)
+    scores = torch.einsum("hd,hsd->hs", q.float(), K) / (D ** 0.5)
+    return torch.einsum("hs,hsd->hd", torch.softmax(scores, dim=-1), V)
+
+
 def quant_weight_perrow(Wf: torch.Tensor):
     """Per-output-row e4m3 quantisation of an fp32 weight matrix: (W_e4m3, w_scale)."""
     amax = Wf.abs().amax(dim=1)

@@ -464,8 +464,9 @@ def _attention_fp8_prefill_then_decode(built_lib, which):
     assert rel_l2(pre, g["want"][:S - 1]) < 0.3
     assert rel_l2(dec, g["want"][S - 1]) < 0.35
     # shim (the reference's own quantiser): per prefill norm and add = 2; decode norm, 4 GEMVs, add = 6
-    # fused: per prefill norm+quantise (2), quantiser (2), add = 5; decode 3 GEMVs with the norm inside, o_proj GEMV + add = 4
-    assert launched == {"stock": 0, "shim": 10, "fused": 14}[which]
+    # fused: per prefill norm+quantise (2), quantiser (2), add = 5; decode 3 GEMVs with the norm inside, the decode
+    # attention (2), o_proj GEMV + add = 6
+    assert launched == {"stock": 0, "shim": 10, "fused": 16}[which]
     return full, pre, dec
 
 
@@ -476,5 +477,8 @@ def test_attention_fp8_prefill_then_decode(built_lib, which):
 
 def test_attention_fp8_fused_equals_unfused_bit_for_bit(built_lib):
     res = {which: _attention_fp8_prefill_then_decode(built_lib, which) for which in ("shim", "fused")}
-    for a, b, name in zip(res["shim"], res["fused"], ("full sequence", "prefill", "decode")):
+    for a, b, name in zip(res["shim"][:2], res["fused"][:2], ("full sequence", "prefill")):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16)), name
+    # the decode step of the fused build also runs this library's decode attention, whose fp32 sums associate differently
+    # from the reference kernel's: equal to bf16 resolution, not necessarily bit for bit
+    assert rel_l2(res["fused"][2], res["shim"][2]) < 1e-2
