@@ -44,6 +44,7 @@ SHAPES = {
     "gemv_up": (12544, 3136),        # up_proj   N = 12544, K = 3136: 3136 weight bytes per output row
     "gemv_down": (3136, 12544),      # down_proj N = 3136,  K = 12544
     "ssm_step": (1, 2 * 96 * 80 * 128 * 4),   # per sequence: the fp32 state [96, 80, 128] read and written once
+    "sdpa_decode": (512, 2 * 8 * 128 * 2),    # per cached token: one K and one V row of each of the 8 KV heads
     # e4m3 activation quantisation (the step after the norm / activation in the FP8 blocks)
     "quantize_fp8": (8192, 3136 * (2 + 2 + 1)),                  # amax pass + quantising pass over [T, 3136]
     "add_rmsnorm_quant_fp8": (8192, 3136 * (2 + 2 + 2 + 2 + 1)),  # x, r -> out_res ; out_res -> e4m3
@@ -89,6 +90,13 @@ def make_case(op: str, T: int, dev):
         sc = torch.rand(T, device=dev) * 0.01
         y = torch.empty(T, dtype=BF, device=dev)
         return lambda: ops.gemv_w8a16(x, W, sc, out=y)
+    if op == "sdpa_decode":
+        H_Q, H_KV = 40, 8
+        q, kn, vn = rn(H_Q, 128).to(BF), rn(H_KV, 128).to(BF), rn(H_KV, 128).to(BF)
+        k, v = rn(H_KV, T + 1, 128).to(BF), rn(H_KV, T + 1, 128).to(BF)
+        o = torch.empty(H_Q, 128, dtype=BF, device=dev)
+        ws = torch.empty(max(16, _lib.load().nmt_sdpa_decode_workspace_bytes(T, H_Q)), dtype=torch.uint8, device=dev)
+        return lambda: ops.sdpa_decode(q, k, v, kn, vn, T, out=o, workspace=ws)
     if op == "ssm_step":
         H, P, N, G = 96, 80, 128, 8
         x, dt = rn(T, H * P).to(BF), (rn(T, H) - 1).to(BF)
@@ -136,8 +144,8 @@ def run_op(op: str, T: int, reps: int, warmup: int, dev, batch: int = 10, graph:
     nbytes = bpt * T
     # enough buffer sets that a launch never finds its tensors in L2 (at most 8; the small per-sequence state of the SSM
     # step, which in a decode step is evicted by 3 GB of weights between two uses, gets as many as that takes)
-    nsets = max(2, min(48 if op == "ssm_step" else 8, -(-2 * L2_BYTES // max(nbytes, 1)) + 1))
-    if op == "ssm_step":
+    nsets = max(2, min(48 if op in ("ssm_step", "sdpa_decode") else 8, -(-2 * L2_BYTES // max(nbytes, 1)) + 1))
+    if op in ("ssm_step", "sdpa_decode"):
         batch = max(batch, nsets)                 # one timed interval walks every set once
     fns = [make_case(op, T, dev) for _ in range(nsets)]
     for i in range(max(warmup, 3)):
@@ -244,7 +252,7 @@ def main() -> None:
             print(json.dumps(run_fixed_cost(op, T, a.reps, f"cuda:{a.device}")), flush=True)
             torch.cuda.empty_cache()
             continue
-        print(json.dumps(run_op(op, T, a.reps, a.warmup, f"cuda:{a.device}", a.batch, a.graph or op.startswith("gemv") or op == "ssm_step")), flush=True)
+        print(json.dumps(run_op(op, T, a.reps, a.warmup, f"cuda:{a.device}", a.batch, a.graph or op.startswith("gemv") or op in ("ssm_step", "sdpa_decode"))), flush=True)
         torch.cuda.empty_cache()
 
 
