@@ -149,10 +149,12 @@ def test_reference_attention_block_matches_its_golden(built_lib, attn_golden, wh
     assert built_lib.nmt_launch_count() - before == (0 if which == "stock" else 4)      # norm + add, twice
 
 
-def test_attention_prefill_then_decode_on_the_drop_in(attn_golden):
+@pytest.mark.parametrize("which", ["shim", "fused"])
+def test_attention_prefill_then_decode_on_the_drop_in(attn_golden, which):
     """The reference's hand-off check (tests/model/test_attention_block.cu:196-243): prefill S-1 tokens into the KV cache,
-    decode token S, compare with row S-1 of the full-sequence golden (rel L2 < 0.1)."""
-    lib, g = load_blocks("shim"), attn_golden
+    decode token S, compare with row S-1 of the full-sequence golden (rel L2 < 0.1).  "shim": the reference's decode
+    attention kernels; "fused": the integration header, where sdpa_decode_bf16 is this library's."""
+    lib, g = load_blocks(which), attn_golden
     S = 40
     b = {k: g[k].to(BF) for k in ("x", "q", "k", "v", "o")}
     kc = torch.zeros(2, S, 128, dtype=BF, device="cuda")
