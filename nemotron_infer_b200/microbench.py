@@ -43,6 +43,8 @@ SHAPES = {
     # single-token decode projections (weight streaming): "tokens" is the number of output rows N here
     "gemv_up": (12544, 3136),        # up_proj   N = 12544, K = 3136: 3136 weight bytes per output row
     "gemv_down": (3136, 12544),      # down_proj N = 3136,  K = 12544
+    "gemv_out": (3136, 7680),        # Mamba-2 out_proj N = 3136, K = 7680 (in_proj: --op gemv_up --tokens 17504)
+    "gemv_o": (3136, 5120),          # attention o_proj N = 3136, K = 5120 (q / k / v: --op gemv_up --tokens 5120 / 1024)
     "ssm_step": (1, 2 * 96 * 80 * 128 * 4),   # per sequence: the fp32 state [96, 80, 128] read and written once
     "sdpa_decode": (512, 2 * 8 * 128 * 2),    # per cached token: one K and one V row of each of the 8 KV heads
     # e4m3 activation quantisation (the step after the norm / activation in the FP8 blocks)
@@ -83,7 +85,7 @@ def make_case(op: str, T: int, dev):
         u = (2 * rn(T, 12544)).to(BF)
         o = torch.empty_like(u)
         return lambda: ops.relu2(u, out=o)
-    if op in ("gemv_up", "gemv_down"):
+    if op.startswith("gemv"):
         K = SHAPES[op][1]
         W = (rn(T, K) * 20).clamp(-448, 448).to(torch.float8_e4m3fn)
         x = rn(K).to(BF)
