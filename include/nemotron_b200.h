@@ -269,6 +269,17 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
 int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, const void* W_e4m3, const float* w_scale,
                          int activation, const void* residual_bf16, void* y_bf16, int64_t N, int64_t K, void* stream);
 
+/* The out_proj of the Mamba-2 decode block with the gated RMSNorm in front of it and the residual add behind it
+ * (model/mamba_block.cuh:504-514: rmsnorm_gated_bf16, gemv_fp8, elementwise add) in one launch:
+ *     out = W @ (gated_rmsnorm(y_in, gate, group_size) * gnorm_w) * w_scale  (+ residual)
+ * Byte-identical to nmt_rmsnorm_gated_bf16 -> nmt_gemv_w8a16_fused(residual) with this library's defaults: every CTA
+ * normalises its own copy of the row, one warp per group, in the stand-alone kernel's order.  y_in, gate bf16 [K],
+ * 16-byte aligned; gnorm_w fp32 [K], 16-byte aligned; K % 64 == 0, K <= 10240, group_size % 8 == 0 and <= 2048,
+ * K % group_size == 0 (NMT_ERR_UNSUPPORTED / NMT_ERR_SHAPE otherwise).  residual may be NULL; out may alias it. */
+int nmt_gemv_w8a16_gated(const void* y_in_bf16, const void* gate_bf16, const float* gnorm_w, float eps, int64_t group_size,
+                         const void* W_e4m3, const float* w_scale, const void* residual_bf16, void* out_bf16, int64_t N,
+                         int64_t K, void* stream);
+
 /* ---- Per-tensor FP8 (e4m3) activation quantisation ---------------------------- */
 
 /* out_fp8 = e4m3(clamp(x / s, +-448)), s = max|x| / 448 (1/448 for an all-zero tensor), *scale_out = s.

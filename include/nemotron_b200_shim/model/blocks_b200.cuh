@@ -291,16 +291,21 @@ inline void mamba_block_decode_fp8(const __nv_bfloat16* input, const Mamba2Block
         bf16* Bm = scratch<bf16>(GN);
         bf16* Cm = scratch<bf16>(GN);
         bf16* y = scratch<bf16>(INTER);
-        bf16* gnormed = scratch<bf16>(INTER);
         ok(nmt_gemv_w8a16_fused(input, w.block_norm_w, EPS, w.in_proj_w, w.in_proj_wscale, 0, nullptr, proj, PROJ, HIDDEN, stream),
            "nmt_gemv_w8a16_fused(norm, in_proj)");
         ok(nmt_causal_conv1d_silu_decode_split_bf16(xbc, w.conv1d_w, w.conv1d_b, x, Bm, Cm, INTER, GN, GN, conv_state, 1, stream),
            "nmt_causal_conv1d_silu_decode_split_bf16");
         ok(nmt_ssm_decode_step_bf16(x, dt, w.A_log, Bm, Cm, w.D, w.dt_bias, ssm_state, y, 1, H, P, N, G, 0.f, FLT_MAX, stream),
            "nmt_ssm_decode_step_bf16");
-        ops::rmsnorm_gated_bf16<G>(y, gnormed, w.gnorm_w, gate, 1, INTER, INTER / G, EPS, stream);
-        ok(nmt_gemv_w8a16_fused(gnormed, nullptr, 0.f, w.out_proj_w, w.out_proj_wscale, 0, input, out, HIDDEN, INTER, stream),
-           "nmt_gemv_w8a16_fused(out_proj, residual)");
+        if constexpr (INTER <= 10240 && (INTER / G) % 8 == 0 && INTER / G <= 2048) {
+            ok(nmt_gemv_w8a16_gated(y, gate, w.gnorm_w, EPS, INTER / G, w.out_proj_w, w.out_proj_wscale, input, out, HIDDEN, INTER,
+                                    stream), "nmt_gemv_w8a16_gated(gated norm, out_proj, residual)");
+        } else {
+            bf16* gnormed = scratch<bf16>(INTER);
+            ops::rmsnorm_gated_bf16<G>(y, gnormed, w.gnorm_w, gate, 1, INTER, INTER / G, EPS, stream);
+            ok(nmt_gemv_w8a16_fused(gnormed, nullptr, 0.f, w.out_proj_w, w.out_proj_wscale, 0, input, out, HIDDEN, INTER, stream),
+               "nmt_gemv_w8a16_fused(out_proj, residual)");
+        }
     }
 }
 

@@ -253,6 +253,9 @@ struct GemvFusion {
     int norm_threads;             // threads per row of the stand-alone norm kernel (its summation order)
     int activation;               // 1: y = relu(y)^2
     const uint16_t* residual;     // non-null: y += residual[row]
+    const uint4* gate;            // non-null: x = gated_rmsnorm(x, gate) * norm_w over groups of group_vecs * 8 columns
+    int group_vecs;               // 16-byte vectors per group
+    float inv_group;              // 1 / columns per group
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -275,7 +278,40 @@ __device__ __forceinline__ int stage_x(const __nv_bfloat16* __restrict__ x, cons
     const int nv = K / 8;                                          // 16-byte vectors of x
     const uint4* xv = reinterpret_cast<const uint4*>(x);
     const bool normed = fu.norm_w != nullptr;                      // block-uniform
-    if (normed) {
+    if (normed && fu.gate) {
+        // The Mamba-2 gated norm in the stand-alone kernel's shape (gated_groupwarp_kernel): one warp per group, lane l
+        // owns vectors l, l + 32, ... of the group, per-lane f32x2 sums in that order, one butterfly - the normalised
+        // bf16 row equals the stand-alone kernel's output bit for bit.  g is recomputed in the second walk instead of
+        // being kept in registers (the weight stream's first two load groups live there at this point).
+        const int gv = fu.group_vecs, ngroups = nv / gv;
+        for (int grp = warp; grp < ngroups; grp += kGemvWarps) {
+            const uint4* yg = xv + (size_t)grp * gv;
+            const uint4* zg = fu.gate + (size_t)grp * gv;
+            float2 acc = make_float2(0.f, 0.f);
+            for (int v = lane; v < gv; v += 32) {
+                float2 py[4], pz[4];
+                unpack8x2(ld_stream(yg + v), py);
+                unpack8x2(ld_stream(zg + v), pz);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 g = __fmul2_rn(py[k], silu2_sfu(pz[k]));
+                    acc = __ffma2_rn(g, g, acc);
+                }
+            }
+            const float ss = warp_sum(acc.x + acc.y);
+            const float rstd = rsqrtf(ss * fu.inv_group + fu.eps);
+            const float* wg = fu.norm_w + (size_t)grp * gv * 8;
+            for (int v = lane; v < gv; v += 32) {
+                float2 py[4], pz[4], g[4];
+                unpack8x2(ld_stream(yg + v), py);
+                unpack8x2(ld_stream(zg + v), pz);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) g[k] = __fmul2_rn(py[k], silu2_sfu(pz[k]));
+                xn[(size_t)grp * gv + v] = scale8(g, rstd, ld_weight4(wg + v * 8), ld_weight4(wg + v * 8 + 4));
+            }
+        }
+        __syncthreads();
+    } else if (normed) {
         const int nt = fu.norm_threads;
         if (threadIdx.x < nt) {
             float2 acc = make_float2(0.f, 0.f);
@@ -577,6 +613,30 @@ int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, con
         if (r != NMT_ERR_UNSUPPORTED) return r;
     }
     return launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int nmt_gemv_w8a16_gated(const void* y_in_bf16, const void* gate_bf16, const float* gnorm_w, float eps, int64_t group_size,
+                         const void* W_e4m3, const float* w_scale, const void* residual_bf16, void* out_bf16, int64_t N, int64_t K,
+                         void* stream) {
+    using namespace nmt;
+    if (N < 0 || K <= 0 || (K % 64) != 0 || N > 0x7fffffff || group_size <= 0 || (group_size % 8) != 0 || (K % group_size) != 0)
+        return NMT_ERR_SHAPE;
+    if (N == 0) return NMT_OK;
+    if (!y_in_bf16 || !gate_bf16 || !gnorm_w || !W_e4m3 || !w_scale || !out_bf16) return NMT_ERR_NULL;
+    if (!aligned16(y_in_bf16) || !aligned16(gate_bf16) || !aligned16(gnorm_w) || !aligned16(W_e4m3) || !aligned4(w_scale) ||
+        (reinterpret_cast<uintptr_t>(out_bf16) & 1u) || (reinterpret_cast<uintptr_t>(residual_bf16) & 1u))
+        return NMT_ERR_ALIGN;
+    // the normalised row lives in shared memory beside x; groups wider than 2048 take another stand-alone kernel
+    if (K > 10240 || group_size > 2048) return NMT_ERR_UNSUPPORTED;
+    GemvFusion fu = {};
+    fu.norm_w = gnorm_w;
+    fu.eps = eps;
+    fu.gate = static_cast<const uint4*>(gate_bf16);
+    fu.group_vecs = static_cast<int>(group_size / 8);
+    fu.inv_group = 1.0f / static_cast<float>(group_size);
+    fu.residual = static_cast<const uint16_t*>(residual_bf16);
+    return launch_gemv_mma_auto(y_in_bf16, W_e4m3, w_scale, out_bf16, static_cast<int>(N), static_cast<int>(K), fu,
                                 static_cast<cudaStream_t>(stream));
 }
 

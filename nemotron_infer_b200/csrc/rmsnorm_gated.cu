@@ -11,27 +11,6 @@
 
 namespace nmt {
 
-// z / (1 + exp(-z)) through the SFU: 2^(-z*log2 e) and an approximate reciprocal, both good to ~2 ulp of
-// fp32, far below the bf16 rounding of the result.  The .ftz forms are single MUFU instructions (the
-// denormal-preserving forms expand into range-scaling sequences that made this kernel issue-bound); the only
-// visible effect is that silu(z) flushes to zero once |silu(z)| < 2^-126 (z below about -87).
-__device__ __forceinline__ float silu_sfu(float z) {
-    float e, rcp;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z * -1.4426950408889634f));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp) : "f"(1.0f + e));
-    return z * rcp;
-}
-// Two at a time: the multiplies and the add run as f32x2 instructions, the two SFU ops stay scalar.
-__device__ __forceinline__ float2 silu2_sfu(const float2& z) {
-    const float2 t = __fmul2_rn(z, make_float2(-1.4426950408889634f, -1.4426950408889634f));
-    float2 e, rcp;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(t.x));
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(t.y));
-    const float2 d = __fadd2_rn(e, make_float2(1.0f, 1.0f));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp.x) : "f"(d.x));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(rcp.y) : "f"(d.y));
-    return __fmul2_rn(z, rcp);
-}
 __device__ __forceinline__ float silu_exact(float z) { return z / (1.0f + expf(-z)); }
 
 // TRACK: also keep the largest |output| (for the e4m3 quantiser that follows in the FP8 Mamba block,

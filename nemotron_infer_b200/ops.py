@@ -211,6 +211,25 @@ def causal_conv1d_silu_decode(xbc: torch.Tensor, w: torch.Tensor, bias: torch.Te
     return outs if split is not None else outs[0]
 
 
+def gemv_w8a16_gated(y_in: torch.Tensor, gate: torch.Tensor, gnorm_w: torch.Tensor, group_size: int, W: torch.Tensor,
+                     w_scale: torch.Tensor, eps: float = 1e-5, residual: torch.Tensor | None = None,
+                     out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = W @ (gated_rmsnorm(y_in, gate, group_size) * gnorm_w) * w_scale (+ residual): the Mamba-2 decode block's gated
+    norm, out_proj and residual add in one launch, byte-identical to the separate ops."""
+    N, K = W.shape
+    out = torch.empty(N, dtype=torch.bfloat16, device=y_in.device) if out is None else out
+    _dev(y_in, gate, gnorm_w, W, w_scale, out)
+    if W.dtype != torch.float8_e4m3fn or any(t.dtype != torch.bfloat16 for t in (y_in, gate, out)) or \
+            gnorm_w.dtype != torch.float32 or w_scale.dtype != torch.float32:
+        raise ValueError("W must be float8_e4m3fn, y_in / gate / out bf16, gnorm_w / w_scale fp32")
+    if y_in.numel() != K or gate.numel() != K or gnorm_w.numel() != K or w_scale.numel() != N or out.numel() != N:
+        raise ValueError("shape mismatch")
+    _lib.check(_lib.load().nmt_gemv_w8a16_gated(y_in.data_ptr(), gate.data_ptr(), gnorm_w.data_ptr(), float(eps), int(group_size),
+                                                W.data_ptr(), w_scale.data_ptr(), residual.data_ptr() if residual is not None else None,
+                                                out.data_ptr(), N, K, _stream()), "gemv_w8a16_gated")
+    return out
+
+
 def sdpa_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor,
                 s_cache: int, out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of one query token [H_Q, 128] over the first `s_cache` positions of the caches [H_KV, cap, 128]; then

@@ -275,3 +275,39 @@ def test_gemv_argument_checks(built_lib):
     assert L.nmt_gemv_w8a16(B, None, B, B, 4, 3136, None) == 1
     assert L.nmt_gemv_w8a16(B, B + 8, B, B, 4, 3136, None) == 2
     assert L.nmt_gemv_w8a16(B, B, B, B, 4, 64000, None) == 5
+
+
+@pytest.mark.parametrize("N,K,gs,with_res", [(3136, 7680, 960, True), (3136, 7680, 960, False), (64, 64, 32, True), (512, 6144, 768, True),
+                                            (130, 1024, 8, True), (77, 2048, 2048, False)])
+def test_gated_norm_gemv_equals_the_separate_ops(ops, N, K, gs, with_res):
+    """nmt_gemv_w8a16_gated = nmt_rmsnorm_gated_bf16 -> nmt_gemv_w8a16_fused(residual), byte for byte (the Mamba-2 decode
+    block's model/mamba_block.cuh:504-514)."""
+    g = torch.Generator().manual_seed(N + K + gs)
+    y = torch.randn(K, generator=g).to(BF).cuda()
+    z = (2 * torch.randn(K, generator=g)).to(BF).cuda()
+    gw = (1 + 0.1 * torch.randn(K, generator=g)).cuda()
+    Wq, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
+    Wq, sc = Wq.cuda(), sc.cuda()
+    res = torch.randn(N, generator=g).to(BF).cuda() if with_res else None
+    normed = ops.rmsnorm_gated(y.view(1, K), z.view(1, K), gw, gs).view(K)
+    want = ops.gemv_w8a16_fused(normed, Wq, sc, residual=res)
+    got = ops.gemv_w8a16_gated(y, z, gw, gs, Wq, sc, residual=res)
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+
+
+def test_gated_norm_gemv_rejections(built_lib):
+    K, N = 1024, 64
+    y = torch.zeros(K, dtype=BF, device="cuda")
+    gw = torch.ones(K, device="cuda")
+    W = torch.zeros(N, K, dtype=torch.float8_e4m3fn, device="cuda")
+    sc = torch.ones(N, device="cuda")
+    out = torch.zeros(N, dtype=BF, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    call = lambda gs, k=K: built_lib.nmt_gemv_w8a16_gated(p(y), p(y), p(gw), 1e-5, gs, p(W), p(sc), None, p(out), N, k, None)  # noqa: E731
+    before = built_lib.nmt_launch_count()
+    assert call(100) == 3            # group size not a multiple of 8
+    assert call(96) == 3             # does not divide K
+    assert call(8, 1000) == 3        # K not a multiple of 64
+    assert built_lib.nmt_gemv_w8a16_gated(p(y), None, p(gw), 1e-5, 128, p(W), p(sc), None, p(out), N, K, None) == 1
+    assert built_lib.nmt_launch_count() == before
