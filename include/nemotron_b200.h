@@ -269,6 +269,20 @@ int nmt_gemv_w8a16(const void* x_bf16, const void* W_e4m3, const float* w_scale,
 int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, const void* W_e4m3, const float* w_scale,
                          int activation, const void* residual_bf16, void* y_bf16, int64_t N, int64_t K, void* stream);
 
+/* The in_proj of the Mamba-2 decode block with the pre-norm in front of it and the single-token conv step behind it
+ * (model/mamba_block.cuh:473-497: rmsnorm_bf16, three gemv_fp8 over consecutive rows of one matrix,
+ * causal_conv1d_decode_bf16, three strided copies) in one launch.  As nmt_gemv_w8a16_fused(x, norm_w, eps, W, w_scale,
+ * 0, NULL, y, N, K), except that the output rows [conv_row_lo, conv_row_lo + n0 + n1 + n2) - the xBC channels - are not
+ * stored in y: each goes, rounded to bf16 as it would have been stored, through the conv step of its channel (conv_w
+ * [channels][4], conv_bias [channels], window conv_state [channels][3] fp32 updated in place: one sequence) and SiLU,
+ * and lands in out0 [n0] | out1 [n1] | out2 [n2].  Byte-identical to nmt_gemv_w8a16_fused followed by
+ * nmt_causal_conv1d_silu_decode_split_bf16 with batch 1.  The other rows (gate, dt) are stored in y as usual.
+ * K % 64 == 0, K <= 10240 with norm_w; conv_w 16-byte aligned. */
+int nmt_gemv_w8a16_fused_conv_step(const void* x_bf16, const float* norm_w, float eps, const void* W_e4m3, const float* w_scale,
+                                   void* y_bf16, int64_t N, int64_t K, int64_t conv_row_lo, const float* conv_w,
+                                   const float* conv_bias, float* conv_state, void* out0, void* out1, void* out2, int64_t n0,
+                                   int64_t n1, int64_t n2, void* stream);
+
 /* The out_proj of the Mamba-2 decode block with the gated RMSNorm in front of it and the residual add behind it
  * (model/mamba_block.cuh:504-514: rmsnorm_gated_bf16, gemv_fp8, elementwise add) in one launch:
  *     out = W @ (gated_rmsnorm(y_in, gate, group_size) * gnorm_w) * w_scale  (+ residual)

@@ -286,15 +286,15 @@ inline void mamba_block_decode_fp8(const __nv_bfloat16* input, const Mamba2Block
         if (B != 1) return mamba_block_decode_fp8_reference<HIDDEN, H, P, N, G, CONV_K>(input, w, conv_state, ssm_state, out, B, stream);
         // gate | xBC | dt are consecutive rows of in_proj (model/mamba_block.cuh:476-481): one GEMV writes all three.
         bf16* proj = scratch<bf16>(PROJ);
-        bf16 *gate = proj, *xbc = proj + INTER, *dt = proj + INTER + CONV_DIM;
+        bf16 *gate = proj, *dt = proj + INTER + CONV_DIM;
         bf16* x = scratch<bf16>(INTER);
         bf16* Bm = scratch<bf16>(GN);
         bf16* Cm = scratch<bf16>(GN);
         bf16* y = scratch<bf16>(INTER);
-        ok(nmt_gemv_w8a16_fused(input, w.block_norm_w, EPS, w.in_proj_w, w.in_proj_wscale, 0, nullptr, proj, PROJ, HIDDEN, stream),
-           "nmt_gemv_w8a16_fused(norm, in_proj)");
-        ok(nmt_causal_conv1d_silu_decode_split_bf16(xbc, w.conv1d_w, w.conv1d_b, x, Bm, Cm, INTER, GN, GN, conv_state, 1, stream),
-           "nmt_causal_conv1d_silu_decode_split_bf16");
+        // the xBC rows of the projection go through the conv step inside the GEMV's epilogue and land in x | B | C
+        ok(nmt_gemv_w8a16_fused_conv_step(input, w.block_norm_w, EPS, w.in_proj_w, w.in_proj_wscale, proj, PROJ, HIDDEN, INTER,
+                                          w.conv1d_w, w.conv1d_b, conv_state, x, Bm, Cm, INTER, GN, GN, stream),
+           "nmt_gemv_w8a16_fused_conv_step(norm, in_proj, conv step)");
         ok(nmt_ssm_decode_step_bf16(x, dt, w.A_log, Bm, Cm, w.D, w.dt_bias, ssm_state, y, 1, H, P, N, G, 0.f, FLT_MAX, stream),
            "nmt_ssm_decode_step_bf16");
         if constexpr (INTER <= 10240 && (INTER / G) % 8 == 0 && INTER / G <= 2048) {

@@ -35,6 +35,7 @@ PROTOTYPES = {
     "nmt_rmsnorm_gated_bf16": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _f, _p]),
     "nmt_rmsnorm_gated_f32": (_int, [_p, _p, _p, _p, _i64, _i64, _i64, _f, _p]),
     "nmt_relu2_bf16": (_int, [_p, _p, _i64, _p]),
+    "nmt_gemv_w8a16_fused_conv_step": (_int, [_p, _p, _f, _p, _p, _p, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "nmt_gemv_w8a16_gated": (_int, [_p, _p, _p, _f, _i64, _p, _p, _p, _p, _i64, _i64, _p]),
     "nmt_sdpa_decode_workspace_bytes": (_i64, [_i64, _i64]),
     "nmt_sdpa_decode_bf16": (_int, [_p, _p, _p, _p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p, _p]),

@@ -256,6 +256,14 @@ struct GemvFusion {
     const uint4* gate;            // non-null: x = gated_rmsnorm(x, gate) * norm_w over groups of group_vecs * 8 columns
     int group_vecs;               // 16-byte vectors per group
     float inv_group;              // 1 / columns per group
+    // non-null conv_state: output rows [conv_lo, conv_lo + conv_dim) are channels of Mamba-2's causal conv; instead of being
+    // stored they go through the single-token conv step (window in conv_state [conv_dim][3] fp32, updated in place) and
+    // SiLU, and land in the x | B | C tensors conv_out[0..2] of conv_n0 / conv_n1 / the remaining channels
+    float* conv_state;
+    const float* conv_w;          // [conv_dim][4]
+    const float* conv_bias;       // [conv_dim]
+    uint16_t* conv_out[3];
+    int conv_lo, conv_dim, conv_n0, conv_n1;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -506,7 +514,29 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __rest
             uint32_t yb = pack_bf16x2((sum * up) * __ldg(w_scale + row), 0.f);
             if (fu.activation == 1) yb = relu2_bf16x2(yb);
             if (fu.residual) yb = add_bf16x2_rn(static_cast<uint32_t>(fu.residual[row]), yb);
-            reinterpret_cast<uint16_t*>(y)[row] = static_cast<uint16_t>(yb & 0xffffu);
+            const int ch = row - fu.conv_lo;
+            if (fu.conv_state && ch >= 0 && ch < fu.conv_dim) {
+                // the conv step of this channel, in the stand-alone kernel's arithmetic (conv1d_silu_decode_split_kernel):
+                // bias, then taps oldest to newest, the bf16-rounded projection as the newest input
+                const float xin = bf16_lo(yb);
+                float* sp = fu.conv_state + (size_t)ch * 3;
+                const float s0 = sp[0], s1 = sp[1], s2 = sp[2];
+                const float4 wt = ld_weight4(fu.conv_w + (size_t)ch * 4);
+                float acc = __ldg(fu.conv_bias + ch);
+                acc = fmaf(wt.x, s0, acc);
+                acc = fmaf(wt.y, s1, acc);
+                acc = fmaf(wt.z, s2, acc);
+                acc = fmaf(wt.w, xin, acc);
+                sp[0] = s1;
+                sp[1] = s2;
+                sp[2] = xin;
+                int col = ch, seg = 0;
+                if (col >= fu.conv_n0) { col -= fu.conv_n0; seg = 1; if (col >= fu.conv_n1) { col -= fu.conv_n1; seg = 2; } }
+                uint16_t* dst = seg == 0 ? fu.conv_out[0] : seg == 1 ? fu.conv_out[1] : fu.conv_out[2];
+                dst[col] = static_cast<uint16_t>(pack_bf16x2(silu_sfu(acc), 0.f) & 0xffffu);
+            } else {
+                reinterpret_cast<uint16_t*>(y)[row] = static_cast<uint16_t>(yb & 0xffffu);
+            }
         }
     }
     if (!early_trigger) pdl_trigger();
@@ -611,6 +641,45 @@ int nmt_gemv_w8a16_fused(const void* x_bf16, const float* norm_w, float eps, con
         const int r = launch_gemv_umma(x_bf16, norm_w, eps, W_e4m3, w_scale, activation, residual_bf16, y_bf16, static_cast<int>(N),
                                        static_cast<int>(K), static_cast<cudaStream_t>(stream));
         if (r != NMT_ERR_UNSUPPORTED) return r;
+    }
+    return launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
+                                static_cast<cudaStream_t>(stream));
+}
+
+int nmt_gemv_w8a16_fused_conv_step(const void* x_bf16, const float* norm_w, float eps, const void* W_e4m3, const float* w_scale,
+                                   void* y_bf16, int64_t N, int64_t K, int64_t conv_row_lo, const float* conv_w,
+                                   const float* conv_bias, float* conv_state, void* out0, void* out1, void* out2, int64_t n0,
+                                   int64_t n1, int64_t n2, void* stream) {
+    using namespace nmt;
+    if (N < 0 || K <= 0 || (K % 64) != 0 || N > 0x7fffffff || n0 < 0 || n1 < 0 || n2 < 0 || conv_row_lo < 0 ||
+        conv_row_lo + n0 + n1 + n2 > N)
+        return NMT_ERR_SHAPE;
+    if (N == 0) return NMT_OK;
+    const int64_t conv_dim = n0 + n1 + n2;
+    if (!x_bf16 || !W_e4m3 || !w_scale || !y_bf16 || (conv_dim > 0 && (!conv_w || !conv_bias || !conv_state)) || (n0 > 0 && !out0) ||
+        (n1 > 0 && !out1) || (n2 > 0 && !out2))
+        return NMT_ERR_NULL;
+    auto odd = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 1u) != 0; };
+    if (!aligned4(x_bf16) || !aligned16(W_e4m3) || !aligned4(w_scale) || odd(y_bf16) || odd(out0) || odd(out1) || odd(out2) ||
+        (norm_w && (!aligned16(x_bf16) || !aligned16(norm_w))) || !aligned16(conv_w) || !aligned4(conv_bias) || !aligned4(conv_state))
+        return NMT_ERR_ALIGN;
+    GemvFusion fu = {};
+    fu.norm_w = norm_w;
+    fu.eps = eps;
+    fu.inv_cols = 1.0f / static_cast<float>(K);
+    fu.norm_threads = default_norm_block(K / 8, false);
+    if (norm_w && (K > 10240 || fu.norm_threads > kGemvWarps * 32 || (K / 8 + fu.norm_threads - 1) / fu.norm_threads > 8)) return NMT_ERR_UNSUPPORTED;
+    if (conv_dim > 0) {
+        fu.conv_state = conv_state;
+        fu.conv_w = conv_w;
+        fu.conv_bias = conv_bias;
+        fu.conv_out[0] = static_cast<uint16_t*>(out0);
+        fu.conv_out[1] = static_cast<uint16_t*>(out1);
+        fu.conv_out[2] = static_cast<uint16_t*>(out2);
+        fu.conv_lo = static_cast<int>(conv_row_lo);
+        fu.conv_dim = static_cast<int>(conv_dim);
+        fu.conv_n0 = static_cast<int>(n0);
+        fu.conv_n1 = static_cast<int>(n1);
     }
     return launch_gemv_mma_auto(x_bf16, W_e4m3, w_scale, y_bf16, static_cast<int>(N), static_cast<int>(K), fu,
                                 static_cast<cudaStream_t>(stream));

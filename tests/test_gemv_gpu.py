@@ -311,3 +311,37 @@ def test_gated_norm_gemv_rejections(built_lib):
     assert call(8, 1000) == 3        # K not a multiple of 64
     assert built_lib.nmt_gemv_w8a16_gated(p(y), None, p(gw), 1e-5, 128, p(W), p(sc), None, p(out), N, K, None) == 1
     assert built_lib.nmt_launch_count() == before
+
+
+@pytest.mark.parametrize("dims", [dict(HID=3136, INTER=7680, GN=1024, H=96), dict(HID=64, INTER=64, GN=32, H=4)])
+def test_in_proj_with_conv_step_equals_the_separate_ops(ops, built_lib, dims):
+    """nmt_gemv_w8a16_fused_conv_step = nmt_gemv_w8a16_fused (norm folded in) -> nmt_causal_conv1d_silu_decode_split_bf16,
+    byte for byte: x | B | C, the conv window, and the gate / dt rows (model/mamba_block.cuh:473-497), over three tokens."""
+    HID, INTER, GN, H = dims["HID"], dims["INTER"], dims["GN"], dims["H"]
+    CONV = INTER + 2 * GN
+    PROJ = INTER + CONV + H
+    g = torch.Generator().manual_seed(HID)
+    nw = (1 + 0.1 * torch.randn(HID, generator=g)).cuda()
+    Wq, sc = og.quant_weight_perrow(0.05 * torch.randn(PROJ, HID, generator=g))
+    Wq, sc = Wq.cuda(), sc.cuda()
+    cw, cb = (0.3 * torch.randn(CONV, 4, generator=g)).cuda(), (0.1 * torch.randn(CONV, generator=g)).cuda()
+    st_a = (0.5 * torch.randn(1, CONV, 3, generator=g)).cuda()
+    st_b = st_a.clone()
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    for _ in range(3):
+        x = torch.randn(HID, generator=g).to(BF).cuda()
+        proj = ops.gemv_w8a16_fused(x, Wq, sc, norm_w=nw)
+        want = ops.causal_conv1d_silu_decode(proj[INTER:INTER + CONV].view(1, CONV), cw, cb, st_a, split=(INTER, GN, GN))
+        y = torch.full((PROJ,), 7.0, dtype=BF, device="cuda")
+        outs = [torch.empty(n, dtype=BF, device="cuda") for n in (INTER, GN, GN)]
+        before = built_lib.nmt_launch_count()
+        assert built_lib.nmt_gemv_w8a16_fused_conv_step(p(x), p(nw), 1e-5, p(Wq), p(sc), p(y), PROJ, HID, INTER, p(cw), p(cb), p(st_b),
+                                                        p(outs[0]), p(outs[1]), p(outs[2]), INTER, GN, GN, None) == 0
+        assert built_lib.nmt_launch_count() - before == 1
+        torch.cuda.synchronize()
+        for got, w in zip(outs, want):
+            assert torch.equal(got.view(torch.int16), w.reshape(-1).view(torch.int16))
+        assert torch.equal(st_a, st_b), "conv window"
+        assert torch.equal(y[:INTER].view(torch.int16), proj[:INTER].view(torch.int16)), "gate rows"
+        assert torch.equal(y[INTER + CONV:].view(torch.int16), proj[INTER + CONV:].view(torch.int16)), "dt rows"
+        assert bool((y[INTER:INTER + CONV].float() == 7.0).all()), "the xBC rows are not stored"
