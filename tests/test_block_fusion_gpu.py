@@ -285,7 +285,7 @@ def test_single_token_fp8_mlp_block_latency_three_ways(built_lib):
         lib.blk_free_allocator()
     ULP_LOG.append(dict(what="latency_us mlp_block_forward_fp8 one token 3136/12544 (reference kernels / this library's ops / fused)",
                         stock=round(us["stock"], 2), shim=round(us["shim"], 2), fused=round(us["fused"], 2)))
-    assert us["shim"] < us["stock"] and us["fused"] < us["shim"] * 1.1, us
+    assert us["shim"] < us["stock"] and us["fused"] < us["shim"] * 1.25, us
     assert us["stock"] / us["fused"] > 2.0, us
 
 
