@@ -487,6 +487,22 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __rest
     uint4* xn = reinterpret_cast<uint4*>(part + (size_t)iters * kGemvWarps * 16);        // K bf16: the normalised x
     const int e = stage_x(x, fu, K, reinterpret_cast<uint8_t*>(xh), xn, s_red);
 
+    // What the epilogue needs from global memory for this thread's first output row (its only one unless a CTA makes more
+    // than 256 / 16 passes) is requested now, so that it is not a dependent load at the very end of the kernel.
+    float first_scale = 0.f;
+    uint32_t first_res = 0u;
+    {
+        const int o = threadIdx.x;
+        if (o < iters * TILES_PER_CTA * R) {
+            const int it = o / (TILES_PER_CTA * R), rest = o % (TILES_PER_CTA * R);
+            const int row = ((it * gridDim.x + blockIdx.x) * TILES_PER_CTA + rest / R) * R + rest % R;
+            if (row < N) {
+                first_scale = __ldg(w_scale + row);
+                if (fu.residual) first_res = fu.residual[row];
+            }
+        }
+    }
+
     // ---- stream: the next groups' loads are in flight while this group is multiplied ----
 #pragma unroll 1
     while (cit < iters) {
@@ -514,9 +530,10 @@ gemv_w8a16_mma_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __rest
 #pragma unroll
                 for (int s2 = 0; s2 < S; ++s2) sum += part[((size_t)it * kGemvWarps + tc * SPLIT + sp) * 16 + s2 * R + r];
             // bf16 result in the low half of a pair, so the epilogues can use the stand-alone kernels' instructions
-            uint32_t yb = pack_bf16x2((sum * up) * __ldg(w_scale + row), 0.f);
+            const bool first = o == static_cast<int>(threadIdx.x);
+            uint32_t yb = pack_bf16x2((sum * up) * (first ? first_scale : __ldg(w_scale + row)), 0.f);
             if (fu.activation == 1) yb = relu2_bf16x2(yb);
-            if (fu.residual) yb = add_bf16x2_rn(static_cast<uint32_t>(fu.residual[row]), yb);
+            if (fu.residual) yb = add_bf16x2_rn(first ? first_res : static_cast<uint32_t>(fu.residual[row]), yb);
             const int ch = row - fu.conv_lo;
             if (fu.conv_state && ch >= 0 && ch < fu.conv_dim) {
                 // the conv step of this channel, in the stand-alone kernel's arithmetic (conv1d_silu_decode_split_kernel):
