@@ -345,3 +345,24 @@ def test_in_proj_with_conv_step_equals_the_separate_ops(ops, built_lib, dims):
         assert torch.equal(y[:INTER].view(torch.int16), proj[:INTER].view(torch.int16)), "gate rows"
         assert torch.equal(y[INTER + CONV:].view(torch.int16), proj[INTER + CONV:].view(torch.int16)), "dt rows"
         assert bool((y[INTER:INTER + CONV].float() == 7.0).all()), "the xBC rows are not stored"
+
+
+def test_conv_step_form_without_conv_rows_is_the_plain_fused_gemv(ops, built_lib):
+    N, K = 200, 1024
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(K, generator=g).to(BF).cuda()
+    nw = (1 + 0.1 * torch.randn(K, generator=g)).cuda()
+    Wq, sc = og.quant_weight_perrow(0.05 * torch.randn(N, K, generator=g))
+    Wq, sc = Wq.cuda(), sc.cuda()
+    want = ops.gemv_w8a16_fused(x, Wq, sc, norm_w=nw)
+    y = torch.empty(N, dtype=BF, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    assert built_lib.nmt_gemv_w8a16_fused_conv_step(p(x), p(nw), 1e-5, p(Wq), p(sc), p(y), N, K, 0, None, None, None, None, None, None,
+                                                    0, 0, 0, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(y.view(torch.int16), want.view(torch.int16))
+    # a conv range that does not fit the rows is refused, and so is a missing window
+    assert built_lib.nmt_gemv_w8a16_fused_conv_step(p(x), p(nw), 1e-5, p(Wq), p(sc), p(y), N, K, 150, p(nw), p(nw), p(nw), p(y), None, None,
+                                                    64, 0, 0, None) == 3
+    assert built_lib.nmt_gemv_w8a16_fused_conv_step(p(x), p(nw), 1e-5, p(Wq), p(sc), p(y), N, K, 0, p(nw), p(nw), None, p(y), None, None,
+                                                    64, 0, 0, None) == 1

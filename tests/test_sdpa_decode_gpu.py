@@ -39,7 +39,7 @@ def _close(got, want, what):
     assert bool((err <= tol).all()), (what, err.max().item(), tol.min().item())
 
 
-@pytest.mark.parametrize("H_Q,H_KV,S,cap", [(40, 8, 512, 1024), (40, 8, 1, 64), (40, 8, 63, 64), (40, 8, 65, 128), (40, 8, 5000, 5001), (40, 8, 40000, 40001),
+@pytest.mark.parametrize("H_Q,H_KV,S,cap", [(40, 8, 512, 1024), (40, 8, 1, 64), (40, 8, 63, 64), (40, 8, 65, 128), (40, 8, 1024, 1025), (40, 8, 1025, 1100), (40, 8, 5000, 5001), (40, 8, 40000, 40001),
                                             (4, 2, 39, 40), (8, 8, 200, 256), (16, 2, 130, 256), (8, 2, 4097, 8192)])
 def test_against_the_oracle(ops, H_Q, H_KV, S, cap):
     c = _case(H_Q, H_KV, cap, seed=H_Q * 100 + S, scale=3.0)        # larger logits: a peaked softmax
